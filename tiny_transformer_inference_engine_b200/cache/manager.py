@@ -59,7 +59,7 @@ class CacheGroup:
     num_pages: int
     entries: List[Tuple[int, int]] = field(default_factory=list)   # (run entry, index of the need in it), in cache-layer order
     allocator: PageAllocator = None
-    kv: Optional[torch.Tensor] = None                         # [layers, 2, pages, Hkv, page, D]
+    kv: Optional[torch.Tensor] = None                         # [layers, planes, pages, Hkv, page, D] (planes: 2 = K and V; 1 = one array that is both)
     tables: Dict[Hashable, List[int]] = field(default_factory=dict)
 
     @property
@@ -75,7 +75,7 @@ class CacheGroup:
 
     def bytes_per_page(self, elem_size: int) -> int:
         # models/model_config.py:84-88, per group
-        return 2 * len(self.entries) * self.page_size * self.need.num_kv_heads * self.need.head_dim * elem_size
+        return self.need.planes * len(self.entries) * self.page_size * self.need.num_kv_heads * self.need.head_dim * elem_size
 
     def pages_of_request(self, num_tokens: int, max_step_tokens: Optional[int]) -> int:
         """The most pages a request of ``num_tokens`` holds at one time: all of them, or - with a window - those
@@ -131,7 +131,7 @@ class CacheManager:
             g.allocator = PageAllocator(g.num_pages)
             if allocate:
                 # zero-initialised like the reference's pool (serving/kv_pool.py:12-16)
-                g.kv = torch.zeros((len(g.entries), 2, g.num_pages, g.need.num_kv_heads, g.page_size,
+                g.kv = torch.zeros((len(g.entries), g.need.planes, g.num_pages, g.need.num_kv_heads, g.page_size,
                                     g.need.head_dim), dtype=self.dtype, device=self.device)
         self.slots = PageAllocator(self.max_slots, reserve_zero=False)
         self.slot_of: Dict[Hashable, int] = {}
@@ -293,7 +293,7 @@ class CacheManager:
                 if (src, k) in self.entry_group:
                     gi, layer = self.entry_group[(src, k)]
                     g = self.groups[gi]
-                    mine.append(PagedKVView(g.kv[layer, 0], g.kv[layer, 1], block_tables[gi], g.page_size, writable))
+                    mine.append(PagedKVView(g.kv[layer, 0], g.kv[layer, g.need.planes - 1], block_tables[gi], g.page_size, writable))
                 else:
                     mine.append(FixedStateView(self.entry_state[(src, k)], writable))
             views.append(mine)

@@ -42,6 +42,19 @@ class ConfigError(ValueError):
     """A config.json that cannot describe a model of the named architecture."""
 
 
+# An architecture whose config.json has keys of its own registers a class here; ``ModelConfig.from_dict`` hands such a
+# config to that class.  The class offers what the engine asks of every configuration: ``architecture``, ``vocab_size``,
+# ``d_model``, ``max_seq_len``, ``eos_token_id``, ``to_dict()`` and ``save(folder)``.
+_CONFIG_CLASSES: Dict[str, type] = {}
+
+
+def register_config(architecture: str):
+    def deco(cls):
+        _CONFIG_CLASSES[architecture] = cls
+        return cls
+    return deco
+
+
 @dataclass(frozen=True)
 class ModelConfig:
     vocab_size: int
@@ -99,6 +112,9 @@ class ModelConfig:
     @classmethod
     def from_dict(cls, raw: Dict[str, Any]) -> "ModelConfig":
         raw = dict(raw)
+        named = raw.get("architecture")
+        if cls is ModelConfig and named in _CONFIG_CLASSES:
+            return _CONFIG_CLASSES[named].from_dict(raw)
         missing = [k for k in _REQUIRED if k not in raw]
         if missing:
             raise ConfigError(f"config.json lacks required key(s) {missing}; required: {list(_REQUIRED)}")

@@ -12,10 +12,12 @@ constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;      // 256 threads, 4x
 
 __global__ void __launch_bounds__(256)
 gemm_f32_kernel(const float* __restrict__ A, const float* __restrict__ W, const float* __restrict__ bias,
-                float* __restrict__ C, int M, int N, int K, int lda, int ldw, int ldc) {
+                float* __restrict__ C, int M, int N, int K, int lda, int ldw, int ldc,
+                long long batch_a, long long batch_w, long long batch_c) {
     __shared__ float As[BK][BM + 4];
     __shared__ float Ws[BK][BN + 4];
     const int tid = threadIdx.x;
+    A += blockIdx.z * batch_a; W += blockIdx.z * batch_w; C += blockIdx.z * batch_c;      // (a batch of products: grid z)
     const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
     const int tx = tid % 16, ty = tid / 16;
     float acc[TM][TN];
@@ -140,7 +142,21 @@ extern "C" int ttie_gemm_f32(const float* A, const float* W, const float* bias, 
     }
     dim3 grid(ceil_div(N, BN), ceil_div(M, BM));
     if (grid.y > 65535) TTIE_FAIL("gemm_f32: M=%d too large for one launch", M);
-    gemm_f32_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(A, W, bias, C, M, N, K, lda, ldw, ldc);
+    gemm_f32_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(A, W, bias, C, M, N, K, lda, ldw, ldc, 0, 0, 0);
     TTIE_CHECK_LAUNCH("gemm_f32");
+    return 0;
+}
+
+// A batch of products of one shape: C[b] = A[b] * W[b]^T, the operands of batch b at b * batch_a / batch_w / batch_c elements
+// (per-head and per-block weights: strided views of one activation matrix on the A side).
+extern "C" int ttie_gemm_f32_batched(const float* A, const float* W, float* C, int B, int M, int N, int K, long long lda,
+                                     long long ldw, long long ldc, long long batch_a, long long batch_w, long long batch_c,
+                                     void* stream) {
+    if (B <= 0 || M <= 0 || N <= 0) return 0;
+    if (K <= 0) TTIE_FAIL("gemm_f32_batched: K must be positive, got %d", K);
+    dim3 grid(ceil_div(N, BN), ceil_div(M, BM), B);
+    if (grid.y > 65535 || B > 65535) TTIE_FAIL("gemm_f32_batched: M=%d, B=%d too large for one launch", M, B);
+    gemm_f32_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(A, W, nullptr, C, M, N, K, (int)lda, (int)ldw, (int)ldc, batch_a, batch_w, batch_c);
+    TTIE_CHECK_LAUNCH("gemm_f32_batched");
     return 0;
 }

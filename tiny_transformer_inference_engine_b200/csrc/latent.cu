@@ -1,0 +1,123 @@
+// Helpers of latent attention: attention whose cache holds, per token, one low-rank latent vector c (RMS-normed) and one
+// rotated key part shared by all heads.  With the key up-projection folded into the query (q' = W_uk^T q) every head
+// attends over the same cache rows [c | rotated part | zero padding], which also serve as the values: the paged attention
+// kernels run it as multi-query attention whose key and value pages are the same array.
+//   latent_store:  proj[t, col0 : col0 + rank + rot]  ->  page row (RMS norm with weight on the first `rank`, rotation of
+//                  the last `rot` by the token's position), all in 32-bit, rounded once when stored
+//   latent_query:  per head [folded query (rank) | rotated query part (rot) | zeros] in the attention kernels' layout
+//   gate_heads:    out[t, h, :] = v[h, t, :] * sigmoid(gate[t, h])
+#include "common.cuh"
+using namespace ttie;
+
+namespace {
+
+// one warp per token
+template <typename T, typename W>
+__global__ void __launch_bounds__(128)
+latent_store_kernel(const T* __restrict__ proj, long long ld, int col0, int T_, int rank, int rot, int width,
+                    const W* __restrict__ norm_w, float eps, const float2* __restrict__ cs, const int* __restrict__ positions,
+                    const int* __restrict__ token_seq, T* __restrict__ pages, const int* __restrict__ block_table, int bt_stride,
+                    int page_size, int num_pages) {
+    TTIE_PDL_ENTRY();
+    const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (t >= T_) return;
+    const T* src = proj + (size_t)t * ld + col0;
+    const int pos = positions[t];
+    const int page = block_table[(size_t)token_seq[t] * bt_stride + pos / page_size];
+    if (page < 0 || page >= num_pages) return;
+    T* dst = pages + ((size_t)page * page_size + pos % page_size) * width;
+    float sq = 0.f;
+    for (int i = lane; i < rank; i += 32) { const float v = to_f32(src[i]); sq += v * v; }
+    sq = warp_sum(sq);
+    const float r = 1.0f / sqrtf(sq / (float)rank + eps);
+    for (int i = lane; i < rank; i += 32) dst[i] = from_f32<T>(to_f32(src[i]) * r * to_f32(norm_w[i]));
+    const int half = rot >> 1;
+    for (int j = lane; j < half; j += 32) {
+        const float2 c = cs[(size_t)t * half + j];
+        const float u = to_f32(src[rank + 2 * j]), v = to_f32(src[rank + 2 * j + 1]);
+        dst[rank + 2 * j] = from_f32<T>(u * c.x - v * c.y);
+        dst[rank + 2 * j + 1] = from_f32<T>(v * c.x + u * c.y);
+    }
+    for (int i = rank + rot + lane; i < width; i += 32) dst[i] = from_f32<T>(0.f);
+}
+
+// q [T, H * (dim + rot)] (row stride ld), folded [H, T, rank] -> out [T, H, width]
+template <typename T>
+__global__ void latent_query_kernel(const T* __restrict__ q, long long ld, const T* __restrict__ folded, int T_, int H, int dim,
+                                    int rank, int rot, int width, const float2* __restrict__ cs, T* __restrict__ out) {
+    TTIE_PDL_ENTRY();
+    const size_t total = (size_t)T_ * H * width;
+    const int half = rot >> 1;
+    for (size_t e = blockIdx.x * (size_t)blockDim.x + threadIdx.x; e < total; e += (size_t)gridDim.x * blockDim.x) {
+        const int i = (int)(e % width);
+        const int h = (int)((e / width) % H);
+        const size_t t = e / ((size_t)width * H);
+        float v = 0.f;
+        if (i < rank) {
+            v = to_f32(folded[((size_t)h * T_ + t) * rank + i]);
+        } else if (i < rank + rot) {
+            const int k = i - rank, j = k >> 1;
+            const T* qr = q + t * ld + (size_t)h * (dim + rot) + dim;
+            const float2 c = cs[t * half + j];
+            const float a = to_f32(qr[2 * j]), b = to_f32(qr[2 * j + 1]);
+            v = (k & 1) ? (b * c.x + a * c.y) : (a * c.x - b * c.y);
+        }
+        out[e] = from_f32<T>(v);
+    }
+}
+
+// v [H, T, vdim]; gate logits gate[t * ld + h]; out [T, H * vdim]
+template <typename T>
+__global__ void gate_heads_kernel(const T* __restrict__ v, const T* __restrict__ gate, long long ld, int T_, int H, int vdim,
+                                  T* __restrict__ out) {
+    TTIE_PDL_ENTRY();
+    const size_t total = (size_t)T_ * H * vdim;
+    for (size_t e = blockIdx.x * (size_t)blockDim.x + threadIdx.x; e < total; e += (size_t)gridDim.x * blockDim.x) {
+        const int j = (int)(e % vdim);
+        const int h = (int)((e / vdim) % H);
+        const size_t t = e / ((size_t)vdim * H);
+        const float g = 1.0f / (1.0f + expf(-to_f32(gate[t * ld + h])));
+        out[e] = from_f32<T>(to_f32(v[((size_t)h * T_ + t) * vdim + j]) * g);
+    }
+}
+
+inline int grid_for(size_t total) { return (int)((total + 255) / 256 < 8192 ? (total + 255) / 256 : 8192); }
+}  // namespace
+
+extern "C" int ttie_latent_store(const void* proj, long long ld, int col0, int T, int rank, int rot, int width, const void* norm_w,
+                                 int w_dtype, float eps, const void* cs, const int* positions, const int* token_seq, void* pages,
+                                 const int* block_table, int bt_stride, int page_size, int num_pages, int dtype, void* stream) {
+    if (T <= 0) return 0;
+    if (rot % 2 || rank <= 0 || width < rank + rot) TTIE_FAIL("latent_store: rank %d, rotated %d, row width %d", rank, rot, width);
+    cudaStream_t s = (cudaStream_t)stream;
+    const int grid = ceil_div(T, 4);
+#define LS(TT, WW) TTIE_LAUNCH((latent_store_kernel<TT, WW>), grid, 128, 0, s, (const TT*)proj, ld, col0, T, rank, rot, width, (const WW*)norm_w, \
+                               eps, (const float2*)cs, positions, token_seq, (TT*)pages, block_table, bt_stride, page_size, num_pages)
+    if (dtype == kF32) { if (w_dtype != kF32) TTIE_FAIL("latent_store: a 32-bit run needs 32-bit norm weights"); LS(float, float); }
+    else if (w_dtype == kF32) LS(__nv_bfloat16, float);
+    else LS(__nv_bfloat16, __nv_bfloat16);
+#undef LS
+    TTIE_CHECK_LAUNCH("latent_store");
+    return 0;
+}
+
+extern "C" int ttie_latent_query(const void* q, long long ld, const void* folded, int T, int H, int dim, int rank, int rot, int width,
+                                 const void* cs, void* out, int dtype, void* stream) {
+    if (T <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int grid = grid_for((size_t)T * H * width);
+    if (dtype == kF32) TTIE_LAUNCH(latent_query_kernel<float>, grid, 256, 0, s, (const float*)q, ld, (const float*)folded, T, H, dim, rank, rot, width, (const float2*)cs, (float*)out);
+    else TTIE_LAUNCH(latent_query_kernel<__nv_bfloat16>, grid, 256, 0, s, (const __nv_bfloat16*)q, ld, (const __nv_bfloat16*)folded, T, H, dim, rank, rot, width, (const float2*)cs, (__nv_bfloat16*)out);
+    TTIE_CHECK_LAUNCH("latent_query");
+    return 0;
+}
+
+extern "C" int ttie_gate_heads(const void* v, const void* gate, long long ld, int T, int H, int vdim, void* out, int dtype, void* stream) {
+    if (T <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int grid = grid_for((size_t)T * H * vdim);
+    if (dtype == kF32) TTIE_LAUNCH(gate_heads_kernel<float>, grid, 256, 0, s, (const float*)v, (const float*)gate, ld, T, H, vdim, (float*)out);
+    else TTIE_LAUNCH(gate_heads_kernel<__nv_bfloat16>, grid, 256, 0, s, (const __nv_bfloat16*)v, (const __nv_bfloat16*)gate, ld, T, H, vdim, (__nv_bfloat16*)out);
+    TTIE_CHECK_LAUNCH("gate_heads");
+    return 0;
+}

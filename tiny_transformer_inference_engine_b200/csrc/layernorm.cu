@@ -1,0 +1,97 @@
+// LayerNorm over the 32-bit residual stream with the scaled residual add fused in (post-norm layers):
+//     s = alpha * x + delta;   x <- (s - mean(s)) / sqrt(mean((s - mean)^2) + eps) * w + b
+// x stays in 32-bit (the stream is rewritten in place) and a copy in the compute dtype is written for the
+// sub-layer that reads it next.  With a row list the rows are gathered and the stream is left alone (the
+// model's last norm at the places whose logits are wanted).  The sum, both moments and the affine step are
+// 32-bit; the variance is the mean of the squared deviations (two passes over the row held in shared memory).
+// delta: none, [R, d] in the compute dtype or in 32-bit, or 32-bit partial sums [S, R, d] of a K-split product.
+#include "common.cuh"
+using namespace ttie;
+
+namespace {
+
+template <typename T, typename W>
+__global__ void __launch_bounds__(256)
+scale_add_layernorm_kernel(float* __restrict__ resid, const T* __restrict__ delta, const float* __restrict__ dpart, int S,
+                           long long part_stride, const int* __restrict__ rows, const W* __restrict__ weight,
+                           const W* __restrict__ bias, T* __restrict__ out, float* __restrict__ out32, int d, float alpha, float eps,
+                           int write_resid) {
+    extern __shared__ float row[];
+    __shared__ float scratch[32];
+    TTIE_PDL_ENTRY();
+    const int r = blockIdx.x;
+    const size_t src = rows ? (size_t)rows[r] : (size_t)r;
+    float* x = resid + src * d;
+    float sum = 0.f;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        float v = alpha * x[i];
+        if (delta) v += to_f32(delta[src * d + i]);
+        for (int s = 0; s < S; ++s) v += dpart[(size_t)s * part_stride + src * d + i];     // fixed order
+        row[i] = v;
+        sum += v;
+    }
+    const float mean = block_sum(sum, scratch) / (float)d;
+    float sq = 0.f;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) { const float c = row[i] - mean; sq += c * c; }
+    const float rstd = 1.0f / sqrtf(block_sum(sq, scratch) / (float)d + eps);
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        const float y = (row[i] - mean) * rstd * to_f32(weight[i]) + (bias ? to_f32(bias[i]) : 0.f);
+        if (write_resid) x[i] = y;
+        if (out) out[(size_t)r * d + i] = from_f32<T>(y);
+        if (out32) out32[(size_t)r * d + i] = y;
+    }
+}
+
+template <typename T>
+__global__ void cast_rows_kernel(const float* __restrict__ in, T* __restrict__ out, size_t n) {
+    TTIE_PDL_ENTRY();
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) out[i] = from_f32<T>(in[i]);
+}
+
+template <typename T, typename W>
+int launch_ln(float* resid, const void* delta, const float* dpart, int S, long long part_stride, const int* rows, const void* w,
+              const void* b, void* out, float* out32, int R, int d, float alpha, float eps, int write_resid, cudaStream_t s) {
+    TTIE_LAUNCH((scale_add_layernorm_kernel<T, W>), R, 256, (size_t)d * sizeof(float), s, resid, (const T*)delta, dpart, S, part_stride, rows,
+                (const W*)w, (const W*)b, (T*)out, out32, d, alpha, eps, write_resid);
+    TTIE_CHECK_LAUNCH("scale_add_layernorm");
+    return 0;
+}
+}  // namespace
+
+// delta_dtype: the dtype code of `delta` (ignored if null); out_dtype: of `out`; w_dtype: of weight and bias.
+extern "C" int ttie_scale_add_layernorm(float* resid, const void* delta, int delta_dtype, const float* dpart, int S, long long part_stride,
+                                        const int* rows, const void* weight, const void* bias, int w_dtype, void* out, int out_dtype,
+                                        int R, int d, float alpha, float eps, int write_resid, void* stream) {
+    if (R <= 0) return 0;
+    if (d <= 0 || (size_t)d * sizeof(float) > 200 * 1024) TTIE_FAIL("layernorm: width %d not supported", d);
+    cudaStream_t s = (cudaStream_t)stream;
+    static bool big = false;
+    if ((size_t)d * sizeof(float) > 48 * 1024 && !big) {
+        cudaFuncSetAttribute(scale_add_layernorm_kernel<float, float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        cudaFuncSetAttribute(scale_add_layernorm_kernel<__nv_bfloat16, float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        cudaFuncSetAttribute(scale_add_layernorm_kernel<__nv_bfloat16, __nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        big = true;
+    }
+    // a 32-bit delta beside a bfloat16 output goes in as one partial sum
+    if (delta && delta_dtype == kF32 && out_dtype == kBF16) {
+        if (S) TTIE_FAIL("layernorm: a 32-bit delta and partial sums together");
+        dpart = (const float*)delta; S = 1; part_stride = 0; delta = nullptr;
+    }
+    if (delta && delta_dtype != out_dtype) TTIE_FAIL("layernorm: delta dtype %d with output dtype %d", delta_dtype, out_dtype);
+    if (out_dtype == kF32) {
+        if (w_dtype != kF32) TTIE_FAIL("layernorm: a 32-bit run needs 32-bit norm weights");
+        return launch_ln<float, float>(resid, delta, dpart, S, part_stride, rows, weight, bias, nullptr, (float*)out, R, d, alpha, eps, write_resid, s);
+    }
+    if (w_dtype == kF32)
+        return launch_ln<__nv_bfloat16, float>(resid, delta, dpart, S, part_stride, rows, weight, bias, out, nullptr, R, d, alpha, eps, write_resid, s);
+    return launch_ln<__nv_bfloat16, __nv_bfloat16>(resid, delta, dpart, S, part_stride, rows, weight, bias, out, nullptr, R, d, alpha, eps, write_resid, s);
+}
+
+extern "C" int ttie_cast_rows(const float* in, void* out, long long n, int out_dtype, void* stream) {
+    if (n <= 0) return 0;
+    const int grid = (int)((n + 255) / 256 < 4096 ? (n + 255) / 256 : 4096);
+    if (out_dtype == kBF16) TTIE_LAUNCH(cast_rows_kernel<__nv_bfloat16>, grid, 256, 0, (cudaStream_t)stream, in, (__nv_bfloat16*)out, (size_t)n);
+    else TTIE_LAUNCH(cast_rows_kernel<float>, grid, 256, 0, (cudaStream_t)stream, in, (float*)out, (size_t)n);
+    TTIE_CHECK_LAUNCH("cast_rows");
+    return 0;
+}

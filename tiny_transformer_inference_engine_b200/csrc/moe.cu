@@ -1,0 +1,251 @@
+// Gated linear units with their constants as parameters, and a routed mixture of experts.
+//   glu:            y = g' * sigmoid(alpha * g') * (u' + shift), g' = min(g, limit), u' = clamp(u, -limit, limit) (limit <= 0:
+//                   no clamp); alpha = 1, shift = 0 is SwiGLU.  32-bit arithmetic, rounded once.
+//   moe_route:      scores s = sigmoid(z) (or softmax-free variants by flag) from 32-bit router logits; experts form equal groups
+//                   of neighbours, a group's score is the sum of its `group_top` largest scores, only experts of the best
+//                   `keep` groups can be chosen; the `top` largest scores among those win (ties: the lower index); weights are
+//                   s * scale, optionally renormalised to sum to `scale`.  One thread per token, all 32-bit.
+//   moe_plan:       counting sort of the (token, choice) pairs by expert, on the device: offsets per expert, position of each
+//                   pair, and a table of row tiles (expert, first row, rows) for the grouped product; nothing is read on the host.
+//   grouped_gemm:   C[pos, :] = A[row_of(pos), :] * W[expert_of_tile]^T for every tile of the table (FFMA, 32-bit accumulation,
+//                   any sizes; operands in the compute dtype).
+//   moe_combine:    out[t, :] = sum_k weight[t, k] * Y[pos(t, k), :] (+ shared[t, :]) in 32-bit, in the order of k.
+#include "common.cuh"
+using namespace ttie;
+
+namespace {
+
+template <typename T>
+__global__ void glu_kernel(const T* __restrict__ gu, long long ld, T* __restrict__ out, int F, size_t total, float alpha, float limit,
+                           float shift) {
+    TTIE_PDL_ENTRY();
+    for (size_t e = blockIdx.x * (size_t)blockDim.x + threadIdx.x; e < total; e += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = e / F;
+        const int f = (int)(e % F);
+        float g = to_f32(gu[t * ld + f]), u = to_f32(gu[t * ld + F + f]);
+        if (limit > 0.f) { g = fminf(g, limit); u = fminf(fmaxf(u, -limit), limit); }
+        out[e] = from_f32<T>(g / (1.0f + expf(-alpha * g)) * (u + shift));
+    }
+}
+
+constexpr int MAX_EXPERTS = 512;
+
+__global__ void moe_route_kernel(const float* __restrict__ logits, int T_, int E, int groups, int keep, int group_top, int top,
+                                 float scale, int renorm, int* __restrict__ idx, float* __restrict__ wts) {
+    extern __shared__ float sm[];                                   // [blockDim.x][E] scores, then [blockDim.x][groups]
+    TTIE_PDL_ENTRY();
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= T_) return;
+    float* s = sm + (size_t)threadIdx.x * (E + groups);
+    float* gs = s + E;
+    const int per = E / groups;
+    for (int e = 0; e < E; ++e) s[e] = 1.0f / (1.0f + expf(-logits[(size_t)t * E + e]));
+    // group scores: the sum of the group's `group_top` largest scores
+    for (int g = 0; g < groups; ++g) {
+        float acc = 0.f;
+        int taken0 = -1, taken1 = -1;                                // (group_top is at most 2 here; more: see the host check)
+        for (int k = 0; k < group_top && k < per; ++k) {
+            int best = -1;
+            for (int e = 0; e < per; ++e) {
+                if (e == taken0 || e == taken1) continue;
+                if (best < 0 || s[g * per + e] > s[g * per + best]) best = e;
+            }
+            acc += s[g * per + best];
+            if (k == 0) taken0 = best; else taken1 = best;
+        }
+        gs[g] = acc;
+    }
+    // the best `keep` groups stay; the others are marked by a negative group score
+    for (int drop = 0; drop < groups - keep; ++drop) {
+        int worst = -1;
+        for (int g = 0; g < groups; ++g)
+            if (gs[g] >= 0.f && (worst < 0 || gs[g] <= gs[worst])) worst = g;      // (<=: among equals the higher index goes)
+        gs[worst] = -1.f;
+    }
+    float total = 0.f;
+    for (int k = 0; k < top; ++k) {
+        int best = -1;
+        for (int e = 0; e < E; ++e) {
+            if (gs[e / per] < 0.f || s[e] < 0.f) continue;
+            if (best < 0 || s[e] > s[best]) best = e;
+        }
+        idx[(size_t)t * top + k] = best;
+        wts[(size_t)t * top + k] = s[best];
+        total += s[best];
+        s[best] = -1.f;                                              // taken
+    }
+    for (int k = 0; k < top; ++k) wts[(size_t)t * top + k] *= renorm ? scale / total : scale;
+}
+
+// one CTA.  pairs P = T * top.  tiles: int32 [max_tiles][4] = (expert, first row, rows, 0); meta[0] = number of tiles.
+__global__ void __launch_bounds__(1024)
+moe_plan_kernel(const int* __restrict__ idx, int P, int E, int tile_rows, int max_tiles, int* __restrict__ offsets,
+                int* __restrict__ pos_of_pair, int* __restrict__ pair_of_pos, int* __restrict__ tiles, int* __restrict__ meta) {
+    __shared__ int count[MAX_EXPERTS], cursor[MAX_EXPERTS];
+    TTIE_PDL_ENTRY();
+    for (int e = threadIdx.x; e < E; e += blockDim.x) count[e] = 0;
+    __syncthreads();
+    for (int p = threadIdx.x; p < P; p += blockDim.x) atomicAdd(&count[idx[p]], 1);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int at = 0, nt = 0;
+        for (int e = 0; e < E; ++e) {
+            offsets[e] = at; cursor[e] = at;
+            for (int r = 0; r < count[e] && nt < max_tiles; r += tile_rows, ++nt) {
+                tiles[4 * nt] = e; tiles[4 * nt + 1] = at + r; tiles[4 * nt + 2] = min(tile_rows, count[e] - r); tiles[4 * nt + 3] = 0;
+            }
+            at += count[e];
+        }
+        offsets[E] = at;
+        meta[0] = nt;
+    }
+    __syncthreads();
+    for (int p = threadIdx.x; p < P; p += blockDim.x) {
+        const int at = atomicAdd(&cursor[idx[p]], 1);
+        pos_of_pair[p] = at;
+        pair_of_pos[at] = p;
+    }
+}
+
+constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;
+
+// A rows: row_of[pos] / row_div (row_of null: pos itself).  W: [E, N, K] with expert stride.  C [P, N].
+template <typename T, typename TO>
+__global__ void __launch_bounds__(256)
+grouped_gemm_kernel(const T* __restrict__ A, long long lda, const int* __restrict__ row_of, int row_div, const T* __restrict__ W,
+                    long long w_stride, long long ldw, TO* __restrict__ C, long long ldc, const int* __restrict__ tiles,
+                    const int* __restrict__ meta, int N, int K) {
+    __shared__ float As[BK][BM + 4];
+    __shared__ float Ws[BK][BN + 4];
+    __shared__ int arow[BM];
+    TTIE_PDL_ENTRY();
+    const int tile = blockIdx.y;
+    if (tile >= meta[0]) return;
+    const int expert = tiles[4 * tile], r0 = tiles[4 * tile + 1], rows = tiles[4 * tile + 2];
+    const int tid = threadIdx.x, n0 = blockIdx.x * BN;
+    if (tid < BM) arow[tid] = tid < rows ? (row_of ? row_of[r0 + tid] / row_div : r0 + tid) : -1;
+    __syncthreads();
+    const T* We = W + (size_t)expert * w_stride;
+    const int tx = tid % 16, ty = tid / 16;
+    float acc[TM][TN];
+#pragma unroll
+    for (int i = 0; i < TM; ++i)
+#pragma unroll
+        for (int j = 0; j < TN; ++j) acc[i][j] = 0.f;
+    for (int k0 = 0; k0 < K; k0 += BK) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int e = tid + i * 256;
+            const int r = e / BK, kk = e % BK;
+            const int gk = k0 + kk, gn = n0 + r, ar = arow[r];
+            As[kk][r] = (ar >= 0 && gk < K) ? to_f32(A[(size_t)ar * lda + gk]) : 0.f;
+            Ws[kk][r] = (gn < N && gk < K) ? to_f32(We[(size_t)gn * ldw + gk]) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < BK; ++kk) {
+            float a[TM], w[TN];
+#pragma unroll
+            for (int i = 0; i < TM; ++i) a[i] = As[kk][ty * TM + i];
+#pragma unroll
+            for (int j = 0; j < TN; ++j) w[j] = Ws[kk][tx * TN + j];
+#pragma unroll
+            for (int i = 0; i < TM; ++i)
+#pragma unroll
+                for (int j = 0; j < TN; ++j) acc[i][j] = fmaf(a[i], w[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < TM; ++i) {
+        const int r = ty * TM + i;
+        if (r >= rows) continue;
+#pragma unroll
+        for (int j = 0; j < TN; ++j) {
+            const int gn = n0 + tx * TN + j;
+            if (gn < N) C[(size_t)(r0 + r) * ldc + gn] = from_f32<TO>(acc[i][j]);
+        }
+    }
+}
+
+template <typename T>
+__global__ void moe_combine_kernel(const float* __restrict__ Y, const int* __restrict__ pos_of_pair, const float* __restrict__ wts,
+                                   const T* __restrict__ shared, int T_, int d, int top, float* __restrict__ out) {
+    TTIE_PDL_ENTRY();
+    const size_t total = (size_t)T_ * d;
+    for (size_t e = blockIdx.x * (size_t)blockDim.x + threadIdx.x; e < total; e += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = e / d;
+        const int i = (int)(e % d);
+        float acc = 0.f;
+        for (int k = 0; k < top; ++k) acc = fmaf(wts[t * top + k], Y[(size_t)pos_of_pair[t * top + k] * d + i], acc);
+        if (shared) acc += to_f32(shared[e]);
+        out[e] = acc;
+    }
+}
+
+inline int grid_for(size_t total) { return (int)((total + 255) / 256 < 8192 ? (total + 255) / 256 : 8192); }
+}  // namespace
+
+extern "C" int ttie_glu(const void* gate_up, long long ld, void* out, int T, int F, float alpha, float limit, float shift, int dtype,
+                        void* stream) {
+    if (T <= 0 || F <= 0) return 0;
+    const size_t total = (size_t)T * F;
+    if (dtype == kF32) TTIE_LAUNCH(glu_kernel<float>, grid_for(total), 256, 0, (cudaStream_t)stream, (const float*)gate_up, ld, (float*)out, F, total, alpha, limit, shift);
+    else TTIE_LAUNCH(glu_kernel<__nv_bfloat16>, grid_for(total), 256, 0, (cudaStream_t)stream, (const __nv_bfloat16*)gate_up, ld, (__nv_bfloat16*)out, F, total, alpha, limit, shift);
+    TTIE_CHECK_LAUNCH("glu");
+    return 0;
+}
+
+extern "C" int ttie_moe_max_experts() { return MAX_EXPERTS; }
+extern "C" int ttie_moe_tile_rows() { return BM; }
+
+extern "C" int ttie_moe_route(const float* logits, int T, int E, int groups, int keep, int group_top, int top, float scale, int renorm,
+                              int* idx, float* wts, void* stream) {
+    if (T <= 0) return 0;
+    if (E < 1 || E > MAX_EXPERTS || groups < 1 || E % groups || keep < 1 || keep > groups || top < 1 || top > keep * (E / groups)
+        || group_top < 1 || group_top > 2)
+        TTIE_FAIL("moe_route: %d experts in %d groups, keep %d, group score of %d, top %d", E, groups, keep, group_top, top);
+    int threads = 64;
+    while (threads > 1 && (size_t)threads * (E + groups) * sizeof(float) > 40 * 1024) threads >>= 1;
+    TTIE_LAUNCH(moe_route_kernel, ceil_div(T, threads), threads, (size_t)threads * (E + groups) * sizeof(float), (cudaStream_t)stream,
+                logits, T, E, groups, keep, group_top, top, scale, renorm, idx, wts);
+    TTIE_CHECK_LAUNCH("moe_route");
+    return 0;
+}
+
+extern "C" int ttie_moe_plan(const int* idx, int P, int E, int max_tiles, int* offsets, int* pos_of_pair, int* pair_of_pos, int* tiles,
+                             int* meta, void* stream) {
+    if (P <= 0) return 0;
+    if (E > MAX_EXPERTS) TTIE_FAIL("moe_plan: %d experts (limit %d)", E, MAX_EXPERTS);
+    TTIE_LAUNCH(moe_plan_kernel, 1, 1024, 0, (cudaStream_t)stream, idx, P, E, BM, max_tiles, offsets, pos_of_pair, pair_of_pos, tiles, meta);
+    TTIE_CHECK_LAUNCH("moe_plan");
+    return 0;
+}
+
+extern "C" int ttie_grouped_gemm(const void* A, long long lda, const int* row_of, int row_div, const void* W, long long w_stride,
+                                 long long ldw, void* C, long long ldc, const int* tiles, const int* meta, int max_tiles, int N, int K,
+                                 int dtype, int out_dtype, void* stream) {
+    if (max_tiles <= 0 || N <= 0) return 0;
+    if (max_tiles > 65535) TTIE_FAIL("grouped_gemm: %d row tiles in one launch", max_tiles);
+    const dim3 grid(ceil_div(N, BN), max_tiles);
+    cudaStream_t s = (cudaStream_t)stream;
+#define GG(TT, TO) TTIE_LAUNCH((grouped_gemm_kernel<TT, TO>), grid, 256, 0, s, (const TT*)A, lda, row_of, row_div > 0 ? row_div : 1, (const TT*)W, \
+                               w_stride, ldw, (TO*)C, ldc, tiles, meta, N, K)
+    if (dtype == kF32 && out_dtype == kF32) GG(float, float);
+    else if (dtype == kBF16 && out_dtype == kBF16) GG(__nv_bfloat16, __nv_bfloat16);
+    else if (dtype == kBF16 && out_dtype == kF32) GG(__nv_bfloat16, float);
+    else TTIE_FAIL("grouped_gemm: operand dtype %d with output dtype %d", dtype, out_dtype);
+#undef GG
+    TTIE_CHECK_LAUNCH("grouped_gemm");
+    return 0;
+}
+
+extern "C" int ttie_moe_combine(const float* Y, const int* pos_of_pair, const float* wts, const void* shared, int T, int d, int top,
+                                float* out, int dtype, void* stream) {
+    if (T <= 0) return 0;
+    const size_t total = (size_t)T * d;
+    if (dtype == kF32) TTIE_LAUNCH(moe_combine_kernel<float>, grid_for(total), 256, 0, (cudaStream_t)stream, Y, pos_of_pair, wts, (const float*)shared, T, d, top, out);
+    else TTIE_LAUNCH(moe_combine_kernel<__nv_bfloat16>, grid_for(total), 256, 0, (cudaStream_t)stream, Y, pos_of_pair, wts, (const __nv_bfloat16*)shared, T, d, top, out);
+    TTIE_CHECK_LAUNCH("moe_combine");
+    return 0;
+}

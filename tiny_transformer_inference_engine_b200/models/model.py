@@ -29,6 +29,7 @@ class Model:
         self.final_norm = build_part("norm", spec.final_norm)
         self.head = build_part("head", spec.head)
         self.run_order = list(spec.run_order)
+        self.after_entry = None
         for e, entry in enumerate(self.run_order):
             if not 0 <= entry.layer < len(self.blocks):
                 raise ValueError(f"run entry {e} names layer {entry.layer}; the model has {len(self.blocks)}")
@@ -66,6 +67,8 @@ class Model:
             owners[id(part)] = part
         for pid, params in per_part.items():
             owners[pid].load(params)
+        if getattr(self.head, "tied_to_embedding", False):
+            self.head.tie(self.embedding)
         tune = getattr(getattr(self, "ops", None), "tune_products", None)
         if tune is not None:                                       # the kernel library may measure which product suits each shape
             tune([w for p in self.parts() for w in p.product_weights() if w is not None])
@@ -97,6 +100,8 @@ class Model:
         stream = ResidualStream(self.embedding.forward(ctx))
         for e, entry in enumerate(self.run_order):
             self.blocks[entry.layer].forward(stream, ctx, cache_views[e])
+            if self.after_entry is not None:                     # (a debugging aid: sees the stream after every run entry)
+                self.after_entry(e, stream)
         x = self.final_norm.norm_rows(stream.resid, stream.delta, ctx.logit_rows, ctx.num_logit_rows)
         if ctx.num_logit_rows == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=ctx.device)

@@ -55,6 +55,25 @@ _SIGNATURES = {
                                 _c_void],
     "ttie_gemm_tc": [_c_void, _c_ll, _c_void, _c_ll, _c_void, _c_void, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void],
     "ttie_gemm_tc_pair": [_c_void, _c_ll, _c_void, _c_ll, _c_void, _c_void, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void],
+    "ttie_scale_add_layernorm": [_c_void, _c_void, _c_int, _c_void, _c_int, _c_ll, _c_void, _c_void, _c_void, _c_int, _c_void, _c_int,
+                                 _c_int, _c_int, _c_float, _c_float, _c_int, _c_void],
+    "ttie_cast_rows": [_c_void, _c_void, _c_ll, _c_int, _c_void],
+    "ttie_latent_store": [_c_void, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void, _c_int, _c_float, _c_void, _c_void, _c_void,
+                          _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_void],
+    "ttie_latent_query": [_c_void, _c_ll, _c_void, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void, _c_void, _c_int, _c_void],
+    "ttie_gate_heads": [_c_void, _c_void, _c_ll, _c_int, _c_int, _c_int, _c_void, _c_int, _c_void],
+    "ttie_gemm_f32_batched": [_c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_ll, _c_ll, _c_ll, _c_ll, _c_ll, _c_void],
+    "ttie_causal_conv": [_c_void, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_void, _c_void, _c_int, _c_void, _c_int, _c_void, _c_void,
+                         _c_void, _c_void, _c_void, _c_int, _c_void],
+    "ttie_rglru_scan": [_c_void, _c_void, _c_void, _c_void, _c_int, _c_void, _c_void, _c_ll, _c_int, _c_void, _c_ll, _c_int, _c_void,
+                        _c_int, _c_void, _c_void, _c_int, _c_void, _c_int, _c_int, _c_int, _c_int, _c_float, _c_void, _c_int, _c_void,
+                        _c_int, _c_void],
+    "ttie_glu": [_c_void, _c_ll, _c_void, _c_int, _c_int, _c_float, _c_float, _c_float, _c_int, _c_void],
+    "ttie_moe_route": [_c_void, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_void, _c_void, _c_void],
+    "ttie_moe_plan": [_c_void, _c_int, _c_int, _c_int, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void],
+    "ttie_grouped_gemm": [_c_void, _c_ll, _c_void, _c_int, _c_void, _c_ll, _c_ll, _c_void, _c_ll, _c_void, _c_void, _c_int, _c_int, _c_int,
+                          _c_int, _c_int, _c_void],
+    "ttie_moe_combine": [_c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_void, _c_int, _c_void],
     "ttie_sample": [_c_void, _c_int, _c_int, _c_void, _c_void, _c_void, _c_void, _c_void],
     "ttie_sample_tuned": [_c_void, _c_int, _c_int, _c_void, _c_void, _c_void, _c_void, _c_int, _c_void],
 }
@@ -789,6 +808,170 @@ class CudaOps:
                 head_dim, max_q_len, float(scale), int(window), num_splits, split_len, _ptr(scratch),
                 self._dt(qkv), self._stream(qkv)), "paged_attention")
         self.launches += 2 if num_splits > 1 else 1
+
+    # ---- post-norm layers
+    def scale_add_layernorm(self, resid, delta, alpha, weight, bias, eps, out=None, rows=None, num_rows=None, write_resid=True):
+        """resid <- LayerNorm(alpha * resid + delta) * weight + bias over the 32-bit stream [R, d]; ``out`` (compute dtype, or
+        None) receives a copy.  ``delta``: None, [R, d] or float32 partial sums [S, R, d].  With ``rows`` the rows are gathered
+        into ``out`` [num_rows, d]."""
+        d = resid.shape[1]
+        R = resid.shape[0] if rows is None else int(num_rows)
+        dp, pp, S, stride, ddt = None, None, 0, 0, 0
+        if delta is not None:
+            if delta.dim() == 3:
+                pp, S, stride = delta.data_ptr(), delta.shape[0], delta.stride(0)
+            else:
+                dp, ddt = delta.data_ptr(), self._dt(delta)
+        odt = self._dt(out) if out is not None else (0 if weight.dtype == torch.float32 and (delta is None or delta.dtype == torch.float32) else 1)
+        self._check(self.lib.ttie_scale_add_layernorm(_ptr(resid), dp, ddt, pp, S, stride, _ptr(rows), _ptr(weight), _ptr(bias),
+                                                      self._dt(weight), _ptr(out), odt, R, d, float(alpha), float(eps),
+                                                      1 if (write_resid and rows is None) else 0, self._stream(resid)),
+                    "scale_add_layernorm")
+        self.launches += 1
+
+    def cast_rows(self, x32, dtype):
+        """A copy of a float32 tensor in ``dtype``."""
+        out = torch.empty(x32.shape, dtype=dtype, device=x32.device)
+        self._check(self.lib.ttie_cast_rows(_ptr(x32), _ptr(out), x32.numel(), _DT[dtype], self._stream(x32)), "cast_rows")
+        self.launches += 1
+        return out
+
+    # ---- latent attention
+    def latent_store(self, proj, col0, rank, rot, norm_weight, eps, cs_table, positions, token_seq, pages, block_table, page_size):
+        """Normalises (RMS, weight) the ``rank`` latent columns of ``proj`` from ``col0``, rotates the ``rot`` columns after
+        them by the tokens' positions and stores the row into ``pages`` [pages, 1, page, width]."""
+        T = proj.shape[0]
+        self._check(self.lib.ttie_latent_store(_ptr(proj), proj.stride(0), int(col0), T, int(rank), int(rot), pages.shape[-1],
+                                               _ptr(norm_weight), self._dt(norm_weight), float(eps), _ptr(cs_table), _ptr(positions),
+                                               _ptr(token_seq), _ptr(pages), _ptr(block_table), block_table.shape[1], int(page_size),
+                                               pages.shape[0], self._dt(proj), self._stream(proj)), "latent_store")
+        self.launches += 1
+
+    def latent_query(self, q, folded, num_heads, dim, rank, rot, width, cs_table):
+        """[T, H, width] rows [folded query | rotated query part | zeros] from q [T, H * (dim + rot)] (a view with a row
+        stride) and folded [H, T, rank]."""
+        T = q.shape[0]
+        out = torch.empty((T, num_heads * width), dtype=q.dtype, device=q.device)
+        self._check(self.lib.ttie_latent_query(_ptr(q), q.stride(0), _ptr(folded), T, num_heads, dim, rank, rot, width, _ptr(cs_table),
+                                               _ptr(out), self._dt(q), self._stream(q)), "latent_query")
+        self.launches += 1
+        return out
+
+    def gate_heads(self, v, gate, num_heads, vdim):
+        """out[t, h, :] = v[h, t, :] * sigmoid(gate[t, h]); v [H, T, vdim], gate a view [T, H] with a row stride."""
+        T = gate.shape[0]
+        out = torch.empty((T, num_heads * vdim), dtype=v.dtype, device=v.device)
+        self._check(self.lib.ttie_gate_heads(_ptr(v), _ptr(gate), gate.stride(0), T, num_heads, vdim, _ptr(out), self._dt(v),
+                                             self._stream(v)), "gate_heads")
+        self.launches += 1
+        return out
+
+    def batched_linear(self, x, w, out_dtype=None):
+        """y[b] = x[b] @ w[b].T for x [B, M, K] (any batch and row strides, unit inner stride) and w [B, N, K] contiguous
+        -> [B, M, N] contiguous.  float32: this package's FFMA kernel; bfloat16: the library's batched product."""
+        B, M, K = x.shape
+        N = w.shape[1]
+        if x.dtype == torch.float32:
+            out = torch.empty((B, M, N), dtype=torch.float32, device=x.device)
+            if x.stride(2) != 1 or w.stride(2) != 1:
+                raise KernelError("batched_linear: inner strides must be 1")
+            self._check(self.lib.ttie_gemm_f32_batched(_ptr(x), _ptr(w), _ptr(out), B, M, N, K, x.stride(1), w.stride(1), N,
+                                                       x.stride(0), w.stride(0), M * N, self._stream(x)), "gemm_f32_batched")
+            self.launches += 1
+            return out
+        if out_dtype is not None and out_dtype != x.dtype:
+            return torch.bmm(x, w.transpose(1, 2), out_dtype=out_dtype)
+        return torch.bmm(x, w.transpose(1, 2))
+
+    # ---- recurrent block
+    def causal_conv(self, xin, col0, width, taps, conv_w, conv_b, state, token_seq, query_start_loc, slot_ids, want_copy):
+        """Per-channel causal convolution over the step's tokens; inputs before the step come from the state rows.
+        Returns (u float32 [T, width], u in the compute dtype or None)."""
+        T = xin.shape[0]
+        u32 = torch.empty((T, width), dtype=torch.float32, device=xin.device)
+        u_c = torch.empty((T, width), dtype=xin.dtype, device=xin.device) if want_copy else None
+        self._check(self.lib.ttie_causal_conv(_ptr(xin), xin.stride(0), int(col0), T, width, taps, _ptr(conv_w), _ptr(conv_b),
+                                              self._dt(conv_w), _ptr(state), state.shape[0], _ptr(token_seq), _ptr(query_start_loc),
+                                              _ptr(slot_ids), _ptr(u32), _ptr(u_c), self._dt(xin), self._stream(xin)), "causal_conv")
+        self.launches += 1
+        return u32, u_c
+
+    def rglru_scan(self, pre, gate_bias_r, gate_bias_i, lam, u32, xin, col_x, ypre, col_y, state, query_start_loc, slot_ids, num_seqs,
+                   width, taps, block, decay_c, max_q_len, num_tokens):
+        """The gated linear recurrence over the step's tokens from the state rows (advanced in place); returns S * gelu(y)
+        in the compute dtype.  Portions longer than a chunk run the chunked form."""
+        T = u32.shape[0]
+        out = torch.empty((T, width), dtype=xin.dtype, device=xin.device)
+        chunk = int(self.lib.ttie_rglru_chunk())
+        ws = ab = None
+        max_chunks = 0
+        if max_q_len > 2 * chunk:
+            max_chunks = num_tokens // chunk + num_seqs
+            ws = torch.empty(2 * max_chunks + num_seqs, dtype=torch.int32, device=xin.device)
+            ab = torch.empty((max_chunks, width, 2), dtype=torch.float32, device=xin.device)
+        self._check(self.lib.ttie_rglru_scan(_ptr(pre), _ptr(gate_bias_r), _ptr(gate_bias_i), _ptr(lam), self._dt(lam), _ptr(u32),
+                                             _ptr(xin), xin.stride(0), int(col_x), _ptr(ypre), ypre.stride(0), int(col_y),
+                                             _ptr(state), state.shape[0], _ptr(query_start_loc), _ptr(slot_ids), num_seqs,
+                                             _ptr(out), T, width, taps, block, float(decay_c), _ptr(ws), max_chunks, _ptr(ab),
+                                             self._dt(xin), self._stream(xin)), "rglru_scan")
+        self.launches += 4 if ws is not None else 1
+        return out
+
+    # ---- gated linear units and routed experts
+    def glu(self, gate_up, hidden, alpha=1.0, limit=0.0, shift=0.0):
+        """g * sigmoid(alpha * g) * (u + shift) with optional clamps, gate_up = [g | u] per row -> [T, hidden]."""
+        T = gate_up.shape[0]
+        out = torch.empty((T, hidden), dtype=gate_up.dtype, device=gate_up.device)
+        self._check(self.lib.ttie_glu(_ptr(gate_up), gate_up.stride(0), _ptr(out), T, hidden, float(alpha), float(limit or 0.0),
+                                      float(shift), self._dt(gate_up), self._stream(gate_up)), "glu")
+        self.launches += 1
+        return out
+
+    def moe_route(self, logits, groups, keep, group_top, top, scale, renorm=False):
+        """(expert ids int32 [T, top], weights float32 [T, top]) from float32 router logits [T, E]."""
+        T, E = logits.shape
+        idx = torch.empty((T, top), dtype=torch.int32, device=logits.device)
+        wts = torch.empty((T, top), dtype=torch.float32, device=logits.device)
+        self._check(self.lib.ttie_moe_route(_ptr(logits), T, E, groups, keep, group_top, top, float(scale), 1 if renorm else 0,
+                                            _ptr(idx), _ptr(wts), self._stream(logits)), "moe_route")
+        self.launches += 1
+        return idx, wts
+
+    def moe_plan(self, idx, num_experts):
+        """Sorts the (token, choice) pairs by expert on the device: a dict with ``pos_of_pair``, ``pair_of_pos``, ``offsets``,
+        the row-tile table and its size bound."""
+        P = idx.numel()
+        tile = int(self.lib.ttie_moe_tile_rows())
+        max_tiles = P // tile + num_experts
+        buf = torch.empty(2 * P + num_experts + 1 + 4 * max_tiles + 4, dtype=torch.int32, device=idx.device)
+        plan = {"pos_of_pair": buf[:P], "pair_of_pos": buf[P:2 * P], "offsets": buf[2 * P:2 * P + num_experts + 1],
+                "tiles": buf[2 * P + num_experts + 1:2 * P + num_experts + 1 + 4 * max_tiles], "meta": buf[-4:], "max_tiles": max_tiles,
+                "pairs": P}
+        self._check(self.lib.ttie_moe_plan(_ptr(idx), P, num_experts, max_tiles, _ptr(plan["offsets"]), _ptr(plan["pos_of_pair"]),
+                                           _ptr(plan["pair_of_pos"]), _ptr(plan["tiles"]), _ptr(plan["meta"]), self._stream(idx)),
+                    "moe_plan")
+        self.launches += 1
+        return plan
+
+    def grouped_linear(self, x, w, plan, gather_div=0, out_dtype=None):
+        """Rows sorted by expert times their expert's matrix: w [E, N, K]; row ``pos`` of the result is
+        x[pair_of_pos[pos] // gather_div] @ w[e].T (``gather_div`` 0: x[pos])."""
+        E, N, K = w.shape
+        out = torch.empty((plan["pairs"], N), dtype=out_dtype or x.dtype, device=x.device)
+        self._check(self.lib.ttie_grouped_gemm(_ptr(x), x.stride(0), _ptr(plan["pair_of_pos"]) if gather_div else None, int(gather_div),
+                                               _ptr(w), w.stride(0), w.stride(1), _ptr(out), N, _ptr(plan["tiles"]), _ptr(plan["meta"]),
+                                               plan["max_tiles"], N, K, self._dt(x), self._dt(out), self._stream(x)), "grouped_gemm")
+        self.launches += 1
+        return out
+
+    def moe_combine(self, y, plan, wts, shared, num_tokens, dim):
+        """float32 [T, d]: the weighted sum of each token's expert rows (+ the shared expert's output)."""
+        out = torch.empty((num_tokens, dim), dtype=torch.float32, device=y.device)
+        top = wts.shape[1]
+        self._check(self.lib.ttie_moe_combine(_ptr(y), _ptr(plan["pos_of_pair"]), _ptr(wts), _ptr(shared), num_tokens, dim, top,
+                                              _ptr(out), self._dt(shared) if shared is not None else 0, self._stream(y)), "moe_combine")
+        self.launches += 1
+        return out
 
     def sample(self, logits, slot_ids, state, out, probs_out=None, ctas_per_row=0):
         """``ctas_per_row``: 0 = chosen from the vocabulary's size; 1, 2, 4 or 8 CTAs (a cluster) share a row."""

@@ -9,7 +9,7 @@ view the cache manager made for it.
 
 Categories and the methods each must have:
 
-``norm``      ``add_norm(resid, delta) -> x``; ``norm_rows(resid, delta, rows) -> x``
+``norm``      ``add_norm(resid, delta) -> x``; ``norm_rows(resid, delta, rows) -> x`` (post-norm blocks: ``scale_add_norm``)
 ``position``  ``rotary_table() -> (inv_freq, style) | None``; ``apply(q, k, positions)``
 ``mixer``     ``cache_need()`` (or ``cache_needs()`` for several); ``forward(x, ctx, cache) -> y``
 ``ffn``       ``forward(x, ctx) -> y``
@@ -53,6 +53,7 @@ class ParamSpec:
     storage: str = "matrix"            # "matrix" | "vector" | "table"
     init: str = "normal"               # random-weights mode: "normal" | "ones" | "zeros"; tables: "randint" | "arange" | "zeros"
     high: Optional[int] = None         # "randint": values are uniform in [0, high)
+    std: Optional[float] = None        # "normal": a standard deviation of this tensor's own (None: the caller's)
 
 
 @dataclass(frozen=True)
@@ -89,6 +90,7 @@ class PagedKVNeed:
     head_dim: int
     window: Optional[int] = None       # None: all keys
     page_size: Optional[int] = None    # None: the engine's page size
+    planes: int = 2                    # 2: keys and values; 1: one array that is both (latent attention), handed out as K and as V
 
 
 @dataclass(frozen=True)
@@ -172,13 +174,15 @@ class ResidualStream:
     """The residual sum in 32-bit plus the last sub-layer's output not yet added to it.
 
     Norm parts add ``delta`` into ``resid`` in the same kernel that normalises, so the
-    sum is formed and kept in 32-bit whatever the compute dtype is.
+    sum is formed and kept in 32-bit whatever the compute dtype is.  ``x`` (post-norm blocks): a copy of
+    ``resid`` in the compute dtype, if a norm kernel has written one (sub-layers there read the stream itself).
     """
-    __slots__ = ("resid", "delta")
+    __slots__ = ("resid", "delta", "x")
 
     def __init__(self, resid: torch.Tensor, delta: Optional[torch.Tensor] = None):
         self.resid = resid
         self.delta = delta
+        self.x = None
 
 
 # --------------------------------------------------------------------------- base classes

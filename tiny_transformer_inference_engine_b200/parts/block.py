@@ -31,3 +31,38 @@ class PreNormBlock(Block):
         a = self.mixer.forward(h, ctx, mixer_cache_argument(self.mixer, caches))
         h = self.ffn_norm.add_norm(stream.resid, a)
         stream.delta = self.ffn.forward(h, ctx)
+
+
+@register_part("block", "post_norm")
+class PostNormBlock(Block):
+    """Norm after the sum: ``x <- norm1(alpha * x + mixer(x))``, then ``x <- norm2(alpha * x + ffn(x))``; the sub-layers
+    read ``x`` itself.  The stream holds ``x`` in 32-bit; each norm kernel forms the scaled sum, normalises, rewrites the
+    stream and hands the next sub-layer a copy in the compute dtype.  A layer without a feed-forward (``ffn`` None) ends
+    after the first norm."""
+
+    def __init__(self, prefix: str, mixer: PartSpec, mixer_norm: PartSpec, ffn, ffn_norm, alpha: float = 1.0):
+        super().__init__(prefix)
+        self.alpha = float(alpha)
+        self.mixer = build_part("mixer", mixer)
+        self.mixer_norm = build_part("norm", mixer_norm)
+        self.ffn = build_part("ffn", ffn) if ffn is not None else None
+        self.ffn_norm = build_part("norm", ffn_norm) if ffn is not None else None
+
+    def children(self):
+        return [p for p in (self.mixer, self.mixer_norm, self.ffn, self.ffn_norm) if p is not None]
+
+    def cache_needs(self):
+        return self.mixer.cache_needs()
+
+    def forward(self, stream: ResidualStream, ctx: StepContext, caches) -> None:
+        if stream.delta is not None:
+            raise ValueError("a post-norm block cannot follow a block that leaves a sum unformed")
+        x = stream.x
+        if x is None:                                               # the first layer: the embedding's rows
+            x = stream.resid if self.dtype == stream.resid.dtype else self.ops.cast_rows(stream.resid, self.dtype)
+        a = self.mixer.forward(x, ctx, mixer_cache_argument(self.mixer, caches))
+        x = self.mixer_norm.scale_add_norm(stream.resid, a, self.alpha)
+        if self.ffn is not None:
+            f = self.ffn.forward(x, ctx)
+            x = self.ffn_norm.scale_add_norm(stream.resid, f, self.alpha)
+        stream.x = x

@@ -49,3 +49,24 @@ class LinearHead(Head):
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         return self.ops.linear(x, self.weight, None, out_dtype=torch.float32)
+
+
+@register_part("head", "tied")
+class TiedHead(Head):
+    """``logits = E x`` with the embedding table E itself: it owns no tensor; the model hands it the embedding's table once
+    the weights are loaded."""
+    tied_to_embedding = True
+
+    def __init__(self, prefix: str, dim: int, vocab_size: int):
+        super().__init__(prefix)
+        self.dim, self.vocab_size = int(dim), int(vocab_size)
+        self.weight = None
+
+    def tie(self, embedding) -> None:
+        self.weight = embedding.table
+
+    def product_weights(self):
+        return [self.weight]
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return self.ops.linear(x, self.weight, None, out_dtype=torch.float32)

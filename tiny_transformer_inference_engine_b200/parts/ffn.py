@@ -8,6 +8,8 @@ The width ``F`` is this part's parameter.
 """
 from __future__ import annotations
 
+from typing import Dict, Optional
+
 import torch
 
 from .base import FeedForward, ParamSpec, StepContext
@@ -43,3 +45,40 @@ class SwiGLU(FeedForward):
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         act = self.ops.linear_swiglu(x, self.w_gu, self.b_gu, self.hidden)        # [T, F]
         return self.ops.linear(act, self.w_down, self.b_down, partial_ok=True)
+
+
+@register_part("ffn", "glu")
+class GLU(FeedForward):
+    """A gated linear unit with its constants as parameters:
+    ``down(g' * sigmoid(alpha * g') * (u' + shift))`` with ``g = gate(x)``, ``u = up(x)``, ``g' = min(g, limit)`` and
+    ``u' = clamp(u, -limit, limit)`` (``limit`` None: no clamps).  ``alpha = 1, shift = 0, limit = None`` is SwiGLU;
+    ``alpha = 1.702, shift = 1`` with a limit is the clamped form some models use.  No biases.  ``names``: relative tensor
+    names of the three matrices."""
+
+    def __init__(self, prefix: str, d_model: int, hidden: int, alpha: float = 1.0, limit: Optional[float] = None,
+                 shift: float = 0.0, names: Optional[Dict[str, str]] = None):
+        super().__init__(prefix)
+        self.d_model, self.hidden = int(d_model), int(hidden)
+        self.alpha, self.limit, self.shift = float(alpha), (None if limit is None else float(limit)), float(shift)
+        if self.limit is not None and self.limit <= 0:
+            raise ValueError(f"limit must be positive or None, got {limit}")
+        self.names = {"gate": "gate", "up": "up", "down": "down"}
+        if names:
+            self.names.update(names)
+        self.w_gu = self.w_down = None
+
+    def param_specs(self):
+        n, d, F = self.names, self.d_model, self.hidden
+        return {n["gate"]: ParamSpec((F, d)), n["up"]: ParamSpec((F, d)), n["down"]: ParamSpec((d, F))}
+
+    def load(self, params):
+        n = self.names
+        self.w_gu = torch.cat([params[n["gate"]], params[n["up"]]], dim=0).contiguous()
+        self.w_down = params[n["down"]].contiguous()
+
+    def product_weights(self):
+        return [self.w_gu, self.w_down]
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, partial_ok: bool = True) -> torch.Tensor:
+        act = self.ops.glu(self.ops.linear(x, self.w_gu, None), self.hidden, self.alpha, self.limit or 0.0, self.shift)
+        return self.ops.linear(act, self.w_down, None, partial_ok=partial_ok)

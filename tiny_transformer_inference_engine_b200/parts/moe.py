@@ -1,0 +1,82 @@
+"""A routed mixture of gated-linear-unit experts with grouped top-k selection and an optional shared expert.
+
+Router: ``z = W_r h`` in 32-bit (``h`` in the compute dtype), scores ``s = sigmoid(z)``.  The experts form ``groups`` equal
+groups of neighbours; a group's score is the sum of its ``group_top`` largest scores, and only experts of the best
+``keep`` groups can be chosen.  Of those the ``top`` largest scores win; their weights are ``s * scale`` (``renorm``:
+divided by their sum first).  The output is the weighted sum of the chosen experts' outputs plus, if there is one, a shared
+expert that every token runs.  An expert is ``down(act(gate h) * up h)`` with the activation's constants as parameters.
+
+On the device, with nothing read on the host (so a step can be captured in a graph): route -> counting sort of the
+(token, choice) pairs by expert -> grouped product gate/up over the sorted rows (rows gathered from the tokens) ->
+activation -> grouped product down -> weighted sum per token in the order of the choices (32-bit).  The expert matrices are
+stacked at load: ``[E, 2F, d]`` and ``[E, d, F]``.
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional
+
+import torch
+
+from .base import FeedForward, ParamSpec, PartSpec, StepContext
+from ..registry import register_part, build_part
+
+
+@register_part("ffn", "grouped_moe")
+class GroupedMoE(FeedForward):
+    def __init__(self, prefix: str, d_model: int, hidden: int, experts: int, top: int, groups: int = 1, keep: int = 1,
+                 group_top: int = 2, scale: float = 1.0, renorm: bool = False, alpha: float = 1.0,
+                 limit: Optional[float] = None, shift: float = 0.0, shared: Optional[PartSpec] = None,
+                 names: Optional[Dict[str, str]] = None):
+        super().__init__(prefix)
+        if experts % groups:
+            raise ValueError(f"{experts} experts do not form {groups} equal groups")
+        if not 1 <= keep <= groups:
+            raise ValueError(f"keep={keep} of {groups} groups")
+        if not 1 <= top <= keep * (experts // groups):
+            raise ValueError(f"top={top} experts cannot be chosen from {keep} groups of {experts // groups}")
+        self.d_model, self.hidden, self.experts, self.top = int(d_model), int(hidden), int(experts), int(top)
+        self.groups, self.keep, self.group_top = int(groups), int(keep), int(group_top)
+        self.scale, self.renorm = float(scale), bool(renorm)
+        self.alpha, self.limit, self.shift = float(alpha), limit, float(shift)
+        self.shared = build_part("ffn", shared) if shared is not None else None
+        self.names = {"router": "router", "expert": "e{}", "gate": "gate", "up": "up", "down": "down"}
+        if names:
+            self.names.update(names)
+
+    def children(self):
+        return [self.shared] if self.shared is not None else []
+
+    def _expert_name(self, e: int, which: str) -> str:
+        return f"{self.names['expert'].format(e)}.{self.names[which]}"
+
+    def param_specs(self):
+        d, F = self.d_model, self.hidden
+        specs = {self.names["router"]: ParamSpec((self.experts, d), std=0.5)}
+        for e in range(self.experts):
+            specs[self._expert_name(e, "gate")] = ParamSpec((F, d))
+            specs[self._expert_name(e, "up")] = ParamSpec((F, d))
+            specs[self._expert_name(e, "down")] = ParamSpec((d, F))
+        return specs
+
+    def load(self, params):
+        E = self.experts
+        self.w_router = params[self.names["router"]].contiguous()
+        self.w_gu = torch.stack([torch.cat([params[self._expert_name(e, "gate")], params[self._expert_name(e, "up")]], dim=0)
+                                 for e in range(E)]).contiguous()                        # [E, 2F, d]
+        self.w_down = torch.stack([params[self._expert_name(e, "down")] for e in range(E)]).contiguous()   # [E, d, F]
+
+    def validate(self, ops, dtype, page_size):
+        limit = getattr(getattr(ops, "lib", None), "ttie_moe_max_experts", None)
+        if limit is not None and self.experts > int(limit()):
+            raise ValueError(f"{self.experts} experts exceed the routing kernels' limit of {int(limit())}")
+
+    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        ops, T = self.ops, x.shape[0]
+        logits = ops.linear(x, self.w_router, None, out_dtype=torch.float32)
+        idx, wts = ops.moe_route(logits, self.groups, self.keep, self.group_top, self.top, self.scale, self.renorm)
+        plan = ops.moe_plan(idx, self.experts)
+        h = ops.grouped_linear(x, self.w_gu, plan, gather_div=self.top)                  # [P, 2F], rows sorted by expert
+        act = ops.glu(h, self.hidden, self.alpha, self.limit or 0.0, self.shift)
+        y = ops.grouped_linear(act, self.w_down, plan, out_dtype=torch.float32)          # [P, d] float32
+        shared = self.shared.forward(x, ctx, partial_ok=False) if self.shared is not None else None
+        return ops.moe_combine(y, plan, wts, shared, T, self.d_model)                    # float32 [T, d]

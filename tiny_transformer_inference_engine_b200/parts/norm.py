@@ -45,3 +45,52 @@ class RMSNorm(Norm):
         if num_rows:
             self.ops.rmsnorm_rows(resid, delta, rows, num_rows, self.weight, self.eps, out)
         return out
+
+
+@register_part("norm", "layernorm")
+class LayerNorm(Norm):
+    """LayerNorm with weight and bias over the 32-bit stream: ``(x - mean) / sqrt(var + eps) * w + b`` with the variance the
+    mean of the squared deviations.  For post-norm blocks the scaled residual add is fused in:
+    ``x <- LN(alpha * x + delta)``; the stream keeps the normalised value in 32-bit and the next sub-layer gets a copy in the
+    compute dtype.  ``names``: relative tensor names of the weight and the bias."""
+
+    def __init__(self, prefix: str, dim: int, eps: float, names: Optional[Dict[str, str]] = None, bias: bool = True):
+        super().__init__(prefix)
+        self.dim, self.eps, self.has_bias = int(dim), float(eps), bool(bias)
+        self.names = {"weight": "weight", "bias": "bias"}
+        if names:
+            self.names.update(names)
+        self.weight = self.bias = None
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        specs = {self.names["weight"]: ParamSpec((self.dim,), storage="vector", init="ones")}
+        if self.has_bias:
+            specs[self.names["bias"]] = ParamSpec((self.dim,), storage="vector", init="zeros")
+        return specs
+
+    def load(self, params):
+        self.weight = params[self.names["weight"]]
+        self.bias = params[self.names["bias"]] if self.has_bias else None
+        if self.bias is not None and self.bias.dtype != self.weight.dtype:
+            self.bias = self.bias.to(self.weight.dtype)
+
+    def validate(self, ops, dtype, page_size):
+        check = getattr(ops, "check_norm", None)
+        if check is not None:
+            check(dtype, self.dim)
+
+    def scale_add_norm(self, resid: torch.Tensor, delta: Optional[torch.Tensor], alpha: float) -> torch.Tensor:
+        """``resid <- LN(alpha * resid + delta)`` in place; returns the normalised rows in the compute dtype (the stream
+        itself in a 32-bit run)."""
+        if self.dtype == torch.float32:
+            self.ops.scale_add_layernorm(resid, delta, alpha, self.weight, self.bias, self.eps, None)
+            return resid
+        out = torch.empty(resid.shape, dtype=self.dtype, device=resid.device)
+        self.ops.scale_add_layernorm(resid, delta, alpha, self.weight, self.bias, self.eps, out)
+        return out
+
+    def norm_rows(self, resid, delta, rows, num_rows) -> torch.Tensor:
+        out = torch.empty((num_rows, self.dim), dtype=self.dtype, device=resid.device)
+        if num_rows:
+            self.ops.scale_add_layernorm(resid, delta, 1.0, self.weight, self.bias, self.eps, out, rows=rows, num_rows=num_rows)
+        return out

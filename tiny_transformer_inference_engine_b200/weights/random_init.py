@@ -46,7 +46,7 @@ def random_tensors(config: ModelConfig, seed: int, std: float = 0.02, perturb_no
             out[name] = t.to(torch.int32).contiguous()
             continue
         if ps.init == "normal":
-            t = torch.randn(ps.shape, generator=gen, dtype=torch.float32, device=device) * std
+            t = torch.randn(ps.shape, generator=gen, dtype=torch.float32, device=device) * (ps.std if ps.std is not None else std)
         elif ps.init == "ones":
             t = torch.ones(ps.shape, dtype=torch.float32, device=device)
             if perturb_norms:
