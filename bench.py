@@ -255,8 +255,206 @@ def run_workload(name, pk, layers=None, split_classes=True):
     return res
 
 
+# ------------------------------------------------------------------------------------------ --design munevik
+def munevik_config(width, heads, layers=4):
+    """A Munevik model at layer sizes that resemble a real model's: latent attention with a 256-value cache row, a
+    recurrent block as wide as the model in blocks of 128, a clamped GLU of 4 x width, and 16 experts of width / 2 (two
+    chosen, from the best two of four groups) beside a shared expert.  Layer order: attention + dense, recurrent + experts,
+    recurrent + experts, attention over the first layer's cache + experts, repeated."""
+    att = {"heads": heads, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 192, "mask": {"size": 1024},
+           "rot": {"base": 10000.0, "dims": 64}, "scale": 192 ** -0.5}
+    rec = {"width": width, "blocks": width // 128, "conv": 4}
+    moe = {"kind": "moe", "expert": {"ff": width // 2}, "shared": {"ff": width},
+           "router": {"experts": 16, "top": 2, "groups": {"count": 4, "keep": 2}, "scale": 1.0}}
+    dense = {"kind": "dense", "ff": 4 * width, "limit": 7.0}
+    out = []
+    for i in range(layers):
+        k = i % 4
+        if k == 0:
+            out.append({"type": "latent_attention", "mixer": dict(att), "mlp": dense})
+        elif k == 3:
+            out.append({"type": "latent_attention", "mixer": dict(att, kv_from=i - 3), "mlp": moe})
+        else:
+            out.append({"type": "rglru", "mixer": dict(rec), "mlp": moe})
+    return {"architecture": "Munevik", "vocab": 32000, "width": width, "postln_alpha": 1.0, "norm": {"eps": 1e-6}, "layers": out,
+            "max_seq_len": 4096}
+
+
+def like_config(width, heads, layers=4):
+    """The closest existing model at equal size: pre-norm multi-query attention blocks with heads of 128 and SwiGLU of 4 x width."""
+    return dict(architecture="mqa_gpt", vocab_size=32000, d_model=width, num_layers=layers, num_heads=width // 128, num_kv_heads=1,
+                hidden_size=4 * width, max_seq_len=4096, rope_theta=10000.0, rms_norm_eps=1e-6, bias=False, dtype="bfloat16")
+
+
+class OpRecorder:
+    """Wraps the kernel library's operations: notes every call of one step (name, arguments), so that each can be timed alone
+    afterwards, and its algorithmic bytes and flops from the shapes."""
+    NAMES = ("embed", "add_rmsnorm", "rmsnorm_rows", "linear", "linear_swiglu", "rope_table", "rope_store", "paged_attention",
+             "scale_add_layernorm", "cast_rows", "latent_store", "latent_query", "gate_heads", "batched_linear", "causal_conv",
+             "rglru_scan", "glu", "moe_route", "moe_plan", "grouped_linear", "moe_combine")
+
+    def __init__(self, ops):
+        self.ops, self.calls, self.orig = ops, [], {}
+
+    def __enter__(self):
+        for n in self.NAMES:
+            fn = getattr(self.ops, n)
+            self.orig[n] = fn
+            setattr(self.ops, n, self._wrap(n, fn))
+        return self
+
+    def __exit__(self, *a):
+        for n, fn in self.orig.items():
+            setattr(self.ops, n, fn)
+
+    def _wrap(self, name, fn):
+        def call(*args, **kw):
+            out = fn(*args, **kw)
+            self.calls.append((name, fn, args, kw, out))
+            return out
+        return call
+
+
+def _tensor_bytes(x):
+    import torch
+    if isinstance(x, torch.Tensor):
+        return x.numel() * x.element_size()
+    if isinstance(x, (list, tuple)):
+        return sum(_tensor_bytes(v) for v in x)
+    if isinstance(x, dict):
+        return sum(_tensor_bytes(v) for v in x.values())
+    return 0
+
+
+def op_cost(name, args, kw, out, kv_lens, window):
+    """(bytes that must move, flops) of one recorded call, from its shapes."""
+    import torch
+    flops = 0
+    if name in ("linear", "linear_swiglu"):
+        x, w = args[0], args[1]
+        flops = 2 * x.shape[0] * w.shape[0] * w.shape[1]
+        return _tensor_bytes([x, w, out]), flops
+    if name == "batched_linear":
+        x, w = args[0], args[1]
+        return _tensor_bytes([w, out]) + x.numel() * x.element_size(), 2 * x.shape[0] * x.shape[1] * w.shape[1] * w.shape[2]
+    if name == "grouped_linear":
+        x, w, plan = args[0], args[1], args[2]
+        rows = plan["pairs"]
+        return _tensor_bytes([w, out]) + rows * w.shape[2] * x.element_size(), 2 * rows * w.shape[1] * w.shape[2]
+    if name == "paged_attention":
+        q, H, Hkv, D, kp, vp = args[0], args[1], args[2], args[3], args[4], args[5]
+        planes = 1 if kp.data_ptr() == vp.data_ptr() else 2
+        vis = [min(L, window + n) if window else L for L, n in kv_lens]
+        kv_bytes = sum(vis) * Hkv * D * kp.element_size() * planes
+        fl = sum(4 * H * D * n * (min(L, window) if window else (L - n / 2)) for L, n in kv_lens)
+        return 2 * q.shape[0] * H * D * q.element_size() + kv_bytes, fl
+    if name in ("rope_store", "latent_store"):
+        x = args[0]
+        return 2 * x.shape[-2] * x.shape[-1] * x.element_size() if name == "rope_store" else _tensor_bytes(x) // 4, 0
+    if name == "embed":
+        return 2 * _tensor_bytes(args[2]), 0
+    tensors = [a for a in list(args) + list(kw.values())]
+    skip = 0
+    if name in ("causal_conv", "rglru_scan"):                   # the state tensor holds every slot: count the step's rows only
+        skip = 0
+    return _tensor_bytes(tensors) + _tensor_bytes(out) - skip, 0
+
+
+def time_ops(eng, entries_fn, pk, kv_lens, window, iters=8):
+    """Runs one step with every operation recorded, then times each recorded call alone (a replayed graph of ``iters`` calls);
+    returns rows (operation, calls, microseconds, fraction of its roofline)."""
+    import torch
+    with OpRecorder(eng.ops) as rec:
+        entries_fn()
+        torch.cuda.synchronize()
+    rows = {}
+    for name, fn, args, kw, out in rec.calls:
+        try:
+            us = eng.ops._graph_time(lambda: fn(*args, **kw), iters) * 1e3 / iters
+        except Exception:                                        # (an operation that cannot be captured alone is timed plainly)
+            torch.cuda.synchronize()
+            us = timed(lambda i: fn(*args, **kw), iters) * 1e3 / iters
+        b, f = op_cost(name, args, kw, out, kv_lens, window)
+        ideal = max(b / (pk["hbm_gbs"] * 1e9), f / (pk["bf16_tflops"] * 1e12)) * 1e6
+        key = name
+        if name in ("linear", "batched_linear", "grouped_linear", "linear_swiglu"):
+            w = args[1]
+            key = f"{name} {list(w.shape)}"
+        r = rows.setdefault(key, {"calls": 0, "us": 0.0, "ideal_us": 0.0})
+        r["calls"] += 1; r["us"] += us; r["ideal_us"] += ideal
+    for r in rows.values():
+        r["frac"] = round(r["ideal_us"] / r["us"], 3) if r["us"] else None
+        r["us"], r["ideal_us"] = round(r["us"], 1), round(r["ideal_us"], 2)
+    return rows
+
+
+def run_design(args, pk):
+    """Prefill and decode throughput of the Munevik design at a few sizes, beside the closest existing model (multi-query GPT)
+    at equal width and depth, with every operation of a step timed alone against its roofline."""
+    import torch
+    from tiny_transformer_inference_engine_b200 import Engine, ModelConfig, EngineConfig, CacheConfig, SchedulerConfig, StepEntry, SamplingParams
+    from tiny_transformer_inference_engine_b200.weights import random_tensors
+    sizes = [(1024, 8), (2048, 16), (4096, 32)] if not args.sizes else [(int(w), int(w) // 128) for w in args.sizes.split(",")]
+    Tp, batch, ctx, K, W = 2048, args.batch, 2048, args.steps, max(args.warmup, 3)
+    report = {}
+    for width, heads in sizes:
+        for label, cfg in (("munevik", munevik_config(width, heads, args.layers or 4)), ("mqa_gpt", like_config(width, heads, args.layers or 4))):
+            mc = ModelConfig.from_dict(cfg)
+            page = 64
+            pages = batch * (ctx // page + 4) + Tp // page + 8
+            ec = EngineConfig(dtype="bfloat16", device="cuda:0", use_cuda_graphs=True,
+                              cache=CacheConfig(block_size=page, num_gpu_blocks=pages),
+                              sched=SchedulerConfig(max_num_seqs=batch + 1, max_num_batched_tokens=4096, cudagraph_batch_sizes=[batch]))
+            eng = Engine(mc, random_tensors(mc, 0, store_dtype="bfloat16", device="cuda:0"), ec)
+            vocab = mc.vocab_size
+            g = torch.Generator().manual_seed(0)
+            ptoks = torch.randint(0, vocab, (Tp,), generator=g).tolist()
+
+            def prefill_once(_=None):
+                eng.manager.admit("p")
+                eng.manager.extend("p", 0, Tp)
+                eng.stepper.step([StepEntry("p", 0, ptoks, [Tp - 1])])
+                eng.manager.release("p")
+
+            for _ in range(3):
+                prefill_once()
+            p_ms = timed(prefill_once, 3) / 3
+            window = 1024 if label == "munevik" else 0
+            p_ops = time_ops(eng, prefill_once, pk, [(Tp, Tp)], window)
+            ms, end_len, launches = decode_kernel_path(eng, batch, ctx - (W + K), K, W, vocab, synthetic_fill=False)
+            # one decode step, eagerly, for the per-operation times
+            rids = [f"d{i}" for i in range(batch)]
+            for rid in rids:
+                eng.manager.admit(rid)
+                eng.manager.extend(rid, 0, ctx)
+            for grp in eng.manager.groups:
+                grp.kv.normal_(0, 0.5)
+            saved, eng.stepper.graph_batch_sizes = eng.stepper.graph_batch_sizes, []
+
+            def decode_once():
+                eng.stepper.step([StepEntry(rid, ctx - 1, [7], [0]) for rid in rids])
+
+            d_ops = time_ops(eng, decode_once, pk, [(ctx, 1)] * batch, window)
+            eng.stepper.graph_batch_sizes = saved
+            for rid in rids:
+                eng.manager.release(rid)
+            report[f"{label}_{width}"] = {
+                "prefill_tokens_per_s": round(Tp / (p_ms / 1e3)), "prefill_ms": round(p_ms, 3),
+                "decode_tokens_per_s": round(batch * K / (ms / 1e3)), "decode_ms_per_step": round(ms / K, 4),
+                "decode_launches_per_step": launches // K, "layers": len(mc.layers) if label == "munevik" else mc.num_layers,
+                "prefill_ops": p_ops, "decode_ops": d_ops}
+            del eng
+            torch.cuda.empty_cache()
+    print(json.dumps({"design": "Munevik", "beside": "mqa_gpt", "dtype": "bf16", "data": "synthetic token ids, random-init weights",
+                      "prefill_tokens": Tp, "decode_batch": batch, "decode_context": ctx, "steps": K, "warmup": W,
+                      "peaks": pk, "sizes": report}))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--design", default=None, choices=("munevik",), help="prefill and decode of this design at a few sizes beside the closest existing model, with per-operation times")
+    ap.add_argument("--sizes", default=None, help="with --design: comma-separated model widths (multiples of 128)")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=8)
@@ -297,6 +495,8 @@ def main():
         args.warmup = 3
 
     import torch
+    if args.design:
+        return run_design(args, peaks())
     if args.only_workload:
         print(json.dumps({args.only_workload: run_workload(args.only_workload, peaks(), args.layers, not args.no_class_split)}))
         return 0
