@@ -46,12 +46,12 @@ template <typename T>
 __global__ void latent_query_kernel(const T* __restrict__ q, long long ld, const T* __restrict__ folded, int T_, int H, int dim,
                                     int rank, int rot, int width, const float2* __restrict__ cs, T* __restrict__ out) {
     TTIE_PDL_ENTRY();
-    const size_t total = (size_t)T_ * H * width;
-    const int half = rot >> 1;
-    for (size_t e = blockIdx.x * (size_t)blockDim.x + threadIdx.x; e < total; e += (size_t)gridDim.x * blockDim.x) {
-        const int i = (int)(e % width);
-        const int h = (int)((e / width) % H);
-        const size_t t = e / ((size_t)width * H);
+    const int half = rot >> 1, per_row = H * width;
+    const int col = blockIdx.x * blockDim.x + threadIdx.x;           // grid: (columns of a token's row, tokens)
+    if (col >= per_row) return;
+    const int h = col / width, i = col - h * width;
+    for (size_t t = blockIdx.y; t < (size_t)T_; t += gridDim.y) {
+        const size_t e = t * per_row + col;
         float v = 0.f;
         if (i < rank) {
             v = to_f32(folded[((size_t)h * T_ + t) * rank + i]);
@@ -71,11 +71,12 @@ template <typename T>
 __global__ void gate_heads_kernel(const T* __restrict__ v, const T* __restrict__ gate, long long ld, int T_, int H, int vdim,
                                   T* __restrict__ out) {
     TTIE_PDL_ENTRY();
-    const size_t total = (size_t)T_ * H * vdim;
-    for (size_t e = blockIdx.x * (size_t)blockDim.x + threadIdx.x; e < total; e += (size_t)gridDim.x * blockDim.x) {
-        const int j = (int)(e % vdim);
-        const int h = (int)((e / vdim) % H);
-        const size_t t = e / ((size_t)vdim * H);
+    const int per_row = H * vdim;
+    const int col = blockIdx.x * blockDim.x + threadIdx.x;           // grid: (columns of a token's row, tokens)
+    if (col >= per_row) return;
+    const int h = col / vdim, j = col - h * vdim;
+    for (size_t t = blockIdx.y; t < (size_t)T_; t += gridDim.y) {
+        const size_t e = t * per_row + col;
         const float g = 1.0f / (1.0f + expf(-to_f32(gate[t * ld + h])));
         out[e] = from_f32<T>(to_f32(v[((size_t)h * T_ + t) * vdim + j]) * g);
     }
@@ -105,7 +106,7 @@ extern "C" int ttie_latent_query(const void* q, long long ld, const void* folded
                                  const void* cs, void* out, int dtype, void* stream) {
     if (T <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
-    const int grid = grid_for((size_t)T * H * width);
+    const dim3 grid(ceil_div(H * width, 256), T < 65535 ? T : 65535);
     if (dtype == kF32) TTIE_LAUNCH(latent_query_kernel<float>, grid, 256, 0, s, (const float*)q, ld, (const float*)folded, T, H, dim, rank, rot, width, (const float2*)cs, (float*)out);
     else TTIE_LAUNCH(latent_query_kernel<__nv_bfloat16>, grid, 256, 0, s, (const __nv_bfloat16*)q, ld, (const __nv_bfloat16*)folded, T, H, dim, rank, rot, width, (const float2*)cs, (__nv_bfloat16*)out);
     TTIE_CHECK_LAUNCH("latent_query");
@@ -115,7 +116,7 @@ extern "C" int ttie_latent_query(const void* q, long long ld, const void* folded
 extern "C" int ttie_gate_heads(const void* v, const void* gate, long long ld, int T, int H, int vdim, void* out, int dtype, void* stream) {
     if (T <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
-    const int grid = grid_for((size_t)T * H * vdim);
+    const dim3 grid(ceil_div(H * vdim, 256), T < 65535 ? T : 65535);
     if (dtype == kF32) TTIE_LAUNCH(gate_heads_kernel<float>, grid, 256, 0, s, (const float*)v, (const float*)gate, ld, T, H, vdim, (float*)out);
     else TTIE_LAUNCH(gate_heads_kernel<__nv_bfloat16>, grid, 256, 0, s, (const __nv_bfloat16*)v, (const __nv_bfloat16*)gate, ld, T, H, vdim, (__nv_bfloat16*)out);
     TTIE_CHECK_LAUNCH("gate_heads");

@@ -42,6 +42,56 @@ scale_add_layernorm_kernel(float* __restrict__ resid, const T* __restrict__ delt
     }
 }
 
+// The same with the row in registers: up to PER elements per thread, every load of the row (stream, delta, weight, bias)
+// asked for before the first reduction, so a row costs one trip to memory and two block reductions.
+template <typename T, typename W, int PER>
+__global__ void __launch_bounds__(1024)
+scale_add_layernorm_reg_kernel(float* __restrict__ resid, const T* __restrict__ delta, const float* __restrict__ dpart, int S,
+                               long long part_stride, const int* __restrict__ rows, const W* __restrict__ weight,
+                               const W* __restrict__ bias, T* __restrict__ out, float* __restrict__ out32, int d, float alpha, float eps,
+                               int write_resid) {
+    __shared__ float scratch[32];
+    TTIE_PDL_ENTRY();
+    const int r = blockIdx.x;
+    const size_t src = rows ? (size_t)rows[r] : (size_t)r;
+    float* x = resid + src * d;
+    float v[PER], w[PER], b[PER];
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+        const int i = threadIdx.x + j * blockDim.x;
+        v[j] = 0.f; w[j] = 0.f; b[j] = 0.f;
+        if (i < d) {
+            v[j] = alpha * x[i];
+            if (delta) v[j] += to_f32(delta[src * d + i]);
+            w[j] = to_f32(weight[i]);
+            b[j] = bias ? to_f32(bias[i]) : 0.f;
+        }
+    }
+    for (int s = 0; s < S; ++s)
+#pragma unroll
+        for (int j = 0; j < PER; ++j) {
+            const int i = threadIdx.x + j * blockDim.x;
+            if (i < d) v[j] += dpart[(size_t)s * part_stride + src * d + i];               // fixed order
+        }
+    float sum = 0.f;
+#pragma unroll
+    for (int j = 0; j < PER; ++j) sum += v[j];
+    const float mean = block_sum(sum, scratch) / (float)d;
+    float sq = 0.f;
+#pragma unroll
+    for (int j = 0; j < PER; ++j) { const float c = (threadIdx.x + j * blockDim.x < d) ? v[j] - mean : 0.f; sq += c * c; }
+    const float rstd = 1.0f / sqrtf(block_sum(sq, scratch) / (float)d + eps);
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+        const int i = threadIdx.x + j * blockDim.x;
+        if (i >= d) continue;
+        const float y = (v[j] - mean) * rstd * w[j] + b[j];
+        if (write_resid) x[i] = y;
+        if (out) out[(size_t)r * d + i] = from_f32<T>(y);
+        if (out32) out32[(size_t)r * d + i] = y;
+    }
+}
+
 template <typename T>
 __global__ void cast_rows_kernel(const float* __restrict__ in, T* __restrict__ out, size_t n) {
     TTIE_PDL_ENTRY();
@@ -51,6 +101,13 @@ __global__ void cast_rows_kernel(const float* __restrict__ in, T* __restrict__ o
 template <typename T, typename W>
 int launch_ln(float* resid, const void* delta, const float* dpart, int S, long long part_stride, const int* rows, const void* w,
               const void* b, void* out, float* out32, int R, int d, float alpha, float eps, int write_resid, cudaStream_t s) {
+    if (d <= 8 * 1024) {
+        const int threads = d <= 1024 ? 128 : d <= 2048 ? 256 : d <= 4096 ? 512 : 1024;
+        TTIE_LAUNCH((scale_add_layernorm_reg_kernel<T, W, 8>), R, threads, 0, s, resid, (const T*)delta, dpart, S, part_stride, rows,
+                    (const W*)w, (const W*)b, (T*)out, out32, d, alpha, eps, write_resid);
+        TTIE_CHECK_LAUNCH("scale_add_layernorm");
+        return 0;
+    }
     TTIE_LAUNCH((scale_add_layernorm_kernel<T, W>), R, 256, (size_t)d * sizeof(float), s, resid, (const T*)delta, dpart, S, part_stride, rows,
                 (const W*)w, (const W*)b, (T*)out, out32, d, alpha, eps, write_resid);
     TTIE_CHECK_LAUNCH("scale_add_layernorm");

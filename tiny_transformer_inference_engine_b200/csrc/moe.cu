@@ -1,7 +1,7 @@
 // Gated linear units with their constants as parameters, and a routed mixture of experts.
 //   glu:            y = g' * sigmoid(alpha * g') * (u' + shift), g' = min(g, limit), u' = clamp(u, -limit, limit) (limit <= 0:
 //                   no clamp); alpha = 1, shift = 0 is SwiGLU.  32-bit arithmetic, rounded once.
-//   moe_route:      scores s = sigmoid(z) (or softmax-free variants by flag) from 32-bit router logits; experts form equal groups
+//   moe_route:      scores s = sigmoid(z) from 32-bit router logits; experts form equal groups
 //                   of neighbours, a group's score is the sum of its `group_top` largest scores, only experts of the best
 //                   `keep` groups can be chosen; the `top` largest scores among those win (ties: the lower index); weights are
 //                   s * scale, optionally renormalised to sum to `scale`.  One thread per token, all 32-bit.
@@ -25,6 +25,32 @@ __global__ void glu_kernel(const T* __restrict__ gu, long long ld, T* __restrict
         float g = to_f32(gu[t * ld + f]), u = to_f32(gu[t * ld + F + f]);
         if (limit > 0.f) { g = fminf(g, limit); u = fminf(fmaxf(u, -limit), limit); }
         out[e] = from_f32<T>(g / (1.0f + expf(-alpha * g)) * (u + shift));
+    }
+}
+
+// bfloat16, 8 values per thread (F and the row stride multiples of 8, 16-byte aligned rows)
+__global__ void glu_vec8_kernel(const __nv_bfloat16* __restrict__ gu, long long ld, __nv_bfloat16* __restrict__ out, int F8, size_t total8,
+                                float alpha, float limit, float shift) {
+    TTIE_PDL_ENTRY();
+    for (size_t e = blockIdx.x * (size_t)blockDim.x + threadIdx.x; e < total8; e += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = e / F8;
+        const int f = (int)(e % F8) * 8;
+        const uint4 gv = *reinterpret_cast<const uint4*>(gu + t * ld + f);
+        const uint4 uv = *reinterpret_cast<const uint4*>(gu + t * ld + (size_t)F8 * 8 + f);
+        const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&gv);
+        const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&uv);
+        uint4 ov;
+        __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&ov);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            float2 g = __bfloat1622float2(g2[i]), u = __bfloat1622float2(u2[i]);
+            if (limit > 0.f) {
+                g.x = fminf(g.x, limit); g.y = fminf(g.y, limit);
+                u.x = fminf(fmaxf(u.x, -limit), limit); u.y = fminf(fmaxf(u.y, -limit), limit);
+            }
+            o2[i] = __floats2bfloat162_rn(g.x / (1.0f + expf(-alpha * g.x)) * (u.x + shift), g.y / (1.0f + expf(-alpha * g.y)) * (u.y + shift));
+        }
+        *reinterpret_cast<uint4*>(out + t * (size_t)F8 * 8 + f) = ov;
     }
 }
 
@@ -168,8 +194,89 @@ grouped_gemm_kernel(const T* __restrict__ A, long long lda, const int* __restric
     }
 }
 
+// ---- few rows (decode steps): every tile's weights are streamed once.  A warp owns GV_ROWS weight rows of the tile's expert,
+// its lanes walk K in 16-byte steps, the tile's activation rows (a few, read by every warp) come through the cache MT at a
+// time; lane-partial sums are added by shuffles in a fixed order.  K a multiple of the vector, rows 16-byte aligned.
+constexpr int GV_WARPS = 8, GV_ROWS = 4;
+template <typename T> struct VecOf;
+template <> struct VecOf<float> { static constexpr int N = 4; using V = float4;
+    static __device__ __forceinline__ void load(const float* p, float* o, bool stream) { const float4 v = stream ? __ldcs((const float4*)p) : __ldg((const float4*)p); o[0] = v.x; o[1] = v.y; o[2] = v.z; o[3] = v.w; } };
+template <> struct VecOf<__nv_bfloat16> { static constexpr int N = 8; using V = uint4;
+    static __device__ __forceinline__ void load(const __nv_bfloat16* p, float* o, bool stream) {
+        const uint4 v = stream ? __ldcs((const uint4*)p) : __ldg((const uint4*)p);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(h[i]); o[2 * i] = f.x; o[2 * i + 1] = f.y; } } };
+
+template <typename T, typename TO, int MT>
+__global__ void __launch_bounds__(GV_WARPS * 32)
+grouped_gemv_kernel(const T* __restrict__ A, long long lda, const int* __restrict__ row_of, int row_div, const T* __restrict__ W,
+                    long long w_stride, long long ldw, TO* __restrict__ C, long long ldc, const int* __restrict__ tiles,
+                    const int* __restrict__ meta, int N, int K) {
+    constexpr int VN = VecOf<T>::N;
+    TTIE_PDL_ENTRY();
+    const int tile = blockIdx.y;
+    if (tile >= meta[0]) return;
+    const int expert = tiles[4 * tile], r0 = tiles[4 * tile + 1], rows = tiles[4 * tile + 2];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n0 = (blockIdx.x * GV_WARPS + warp) * GV_ROWS;
+    if (n0 >= N) return;
+    const T* wrow[GV_ROWS];
+#pragma unroll
+    for (int r = 0; r < GV_ROWS; ++r) wrow[r] = W + (size_t)expert * w_stride + (size_t)min(n0 + r, N - 1) * ldw;
+    for (int m0 = 0; m0 < rows; m0 += MT) {
+        const T* arow[MT];
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+            const int pos = r0 + min(m0 + m, rows - 1);
+            arow[m] = A + (size_t)(row_of ? row_of[pos] / row_div : pos) * lda;
+        }
+        float acc[MT][GV_ROWS];
+#pragma unroll
+        for (int m = 0; m < MT; ++m)
+#pragma unroll
+            for (int r = 0; r < GV_ROWS; ++r) acc[m][r] = 0.f;
+        for (int k = lane * VN; k < K; k += 32 * VN) {
+            float w[GV_ROWS][VN], x[MT][VN];
+#pragma unroll
+            for (int r = 0; r < GV_ROWS; ++r) VecOf<T>::load(wrow[r] + k, w[r], m0 + MT >= rows);
+#pragma unroll
+            for (int m = 0; m < MT; ++m) VecOf<T>::load(arow[m] + k, x[m], false);
+#pragma unroll
+            for (int m = 0; m < MT; ++m)
+#pragma unroll
+                for (int r = 0; r < GV_ROWS; ++r)
+#pragma unroll
+                    for (int i = 0; i < VN; ++i) acc[m][r] = fmaf(x[m][i], w[r][i], acc[m][r]);
+        }
+#pragma unroll
+        for (int m = 0; m < MT; ++m)
+#pragma unroll
+            for (int r = 0; r < GV_ROWS; ++r) acc[m][r] = warp_sum(acc[m][r]);
+        if (lane == 0) {
+#pragma unroll
+            for (int m = 0; m < MT; ++m)
+#pragma unroll
+                for (int r = 0; r < GV_ROWS; ++r)
+                    if (m0 + m < rows && n0 + r < N) C[(size_t)(r0 + m0 + m) * ldc + n0 + r] = from_f32<TO>(acc[m][r]);
+        }
+    }
+}
+
+// rows sorted by expert, gathered from the tokens: out[pos, :] = x[row_of[pos] / row_div, :]
 template <typename T>
-__global__ void moe_combine_kernel(const float* __restrict__ Y, const int* __restrict__ pos_of_pair, const float* __restrict__ wts,
+__global__ void gather_rows_kernel(const T* __restrict__ x, long long ldx, const int* __restrict__ row_of, int row_div, int rows, int d,
+                                   T* __restrict__ out) {
+    TTIE_PDL_ENTRY();
+    const size_t total = (size_t)rows * d;
+    for (size_t e = blockIdx.x * (size_t)blockDim.x + threadIdx.x; e < total; e += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = e / d;
+        out[e] = x[(size_t)(row_of[r] / row_div) * ldx + (e % d)];
+    }
+}
+
+template <typename T, typename TY>
+__global__ void moe_combine_kernel(const TY* __restrict__ Y, const int* __restrict__ pos_of_pair, const float* __restrict__ wts,
                                    const T* __restrict__ shared, int T_, int d, int top, float* __restrict__ out) {
     TTIE_PDL_ENTRY();
     const size_t total = (size_t)T_ * d;
@@ -177,7 +284,7 @@ __global__ void moe_combine_kernel(const float* __restrict__ Y, const int* __res
         const size_t t = e / d;
         const int i = (int)(e % d);
         float acc = 0.f;
-        for (int k = 0; k < top; ++k) acc = fmaf(wts[t * top + k], Y[(size_t)pos_of_pair[t * top + k] * d + i], acc);
+        for (int k = 0; k < top; ++k) acc = fmaf(wts[t * top + k], to_f32(Y[(size_t)pos_of_pair[t * top + k] * d + i]), acc);
         if (shared) acc += to_f32(shared[e]);
         out[e] = acc;
     }
@@ -190,6 +297,12 @@ extern "C" int ttie_glu(const void* gate_up, long long ld, void* out, int T, int
                         void* stream) {
     if (T <= 0 || F <= 0) return 0;
     const size_t total = (size_t)T * F;
+    if (dtype == kBF16 && F % 8 == 0 && ld % 8 == 0 && (((uintptr_t)gate_up | (uintptr_t)out) & 15) == 0) {
+        TTIE_LAUNCH(glu_vec8_kernel, grid_for(total / 8), 256, 0, (cudaStream_t)stream, (const __nv_bfloat16*)gate_up, ld, (__nv_bfloat16*)out, F / 8,
+                    total / 8, alpha, limit, shift);
+        TTIE_CHECK_LAUNCH("glu");
+        return 0;
+    }
     if (dtype == kF32) TTIE_LAUNCH(glu_kernel<float>, grid_for(total), 256, 0, (cudaStream_t)stream, (const float*)gate_up, ld, (float*)out, F, total, alpha, limit, shift);
     else TTIE_LAUNCH(glu_kernel<__nv_bfloat16>, grid_for(total), 256, 0, (cudaStream_t)stream, (const __nv_bfloat16*)gate_up, ld, (__nv_bfloat16*)out, F, total, alpha, limit, shift);
     TTIE_CHECK_LAUNCH("glu");
@@ -224,11 +337,24 @@ extern "C" int ttie_moe_plan(const int* idx, int P, int E, int max_tiles, int* o
 
 extern "C" int ttie_grouped_gemm(const void* A, long long lda, const int* row_of, int row_div, const void* W, long long w_stride,
                                  long long ldw, void* C, long long ldc, const int* tiles, const int* meta, int max_tiles, int N, int K,
-                                 int dtype, int out_dtype, void* stream) {
+                                 int dtype, int out_dtype, int few_rows, void* stream) {
     if (max_tiles <= 0 || N <= 0) return 0;
     if (max_tiles > 65535) TTIE_FAIL("grouped_gemm: %d row tiles in one launch", max_tiles);
-    const dim3 grid(ceil_div(N, BN), max_tiles);
     cudaStream_t s = (cudaStream_t)stream;
+    const int vn = dtype == kF32 ? 4 : 8, esz = dtype == kF32 ? 4 : 2;
+    if (few_rows && K % vn == 0 && lda % vn == 0 && ldw % vn == 0 && w_stride % vn == 0 && (((uintptr_t)A | (uintptr_t)W) & 15) == 0 && esz) {
+        const dim3 g(ceil_div(N, GV_WARPS * GV_ROWS), max_tiles);
+#define GV(TT, TO) TTIE_LAUNCH((grouped_gemv_kernel<TT, TO, 4>), g, GV_WARPS * 32, 0, s, (const TT*)A, lda, row_of, row_div > 0 ? row_div : 1, (const TT*)W, \
+                               w_stride, ldw, (TO*)C, ldc, tiles, meta, N, K)
+        if (dtype == kF32 && out_dtype == kF32) GV(float, float);
+        else if (dtype == kBF16 && out_dtype == kBF16) GV(__nv_bfloat16, __nv_bfloat16);
+        else if (dtype == kBF16 && out_dtype == kF32) GV(__nv_bfloat16, float);
+        else TTIE_FAIL("grouped_gemm: operand dtype %d with output dtype %d", dtype, out_dtype);
+#undef GV
+        TTIE_CHECK_LAUNCH("grouped_gemm (few rows)");
+        return 0;
+    }
+    const dim3 grid(ceil_div(N, BN), max_tiles);
 #define GG(TT, TO) TTIE_LAUNCH((grouped_gemm_kernel<TT, TO>), grid, 256, 0, s, (const TT*)A, lda, row_of, row_div > 0 ? row_div : 1, (const TT*)W, \
                                w_stride, ldw, (TO*)C, ldc, tiles, meta, N, K)
     if (dtype == kF32 && out_dtype == kF32) GG(float, float);
@@ -240,12 +366,25 @@ extern "C" int ttie_grouped_gemm(const void* A, long long lda, const int* row_of
     return 0;
 }
 
-extern "C" int ttie_moe_combine(const float* Y, const int* pos_of_pair, const float* wts, const void* shared, int T, int d, int top,
+// dtype: of `shared`; y_dtype: of Y
+extern "C" int ttie_gather_rows(const void* x, long long ldx, const int* row_of, int row_div, int rows, int d, void* out, int dtype, void* stream) {
+    if (rows <= 0) return 0;
+    const size_t total = (size_t)rows * d;
+    if (dtype == kF32) TTIE_LAUNCH(gather_rows_kernel<float>, grid_for(total), 256, 0, (cudaStream_t)stream, (const float*)x, ldx, row_of, row_div > 0 ? row_div : 1, rows, d, (float*)out);
+    else TTIE_LAUNCH(gather_rows_kernel<__nv_bfloat16>, grid_for(total), 256, 0, (cudaStream_t)stream, (const __nv_bfloat16*)x, ldx, row_of, row_div > 0 ? row_div : 1, rows, d, (__nv_bfloat16*)out);
+    TTIE_CHECK_LAUNCH("gather_rows");
+    return 0;
+}
+
+extern "C" int ttie_moe_combine(const void* Y, int y_dtype, const int* pos_of_pair, const float* wts, const void* shared, int T, int d, int top,
                                 float* out, int dtype, void* stream) {
     if (T <= 0) return 0;
     const size_t total = (size_t)T * d;
-    if (dtype == kF32) TTIE_LAUNCH(moe_combine_kernel<float>, grid_for(total), 256, 0, (cudaStream_t)stream, Y, pos_of_pair, wts, (const float*)shared, T, d, top, out);
-    else TTIE_LAUNCH(moe_combine_kernel<__nv_bfloat16>, grid_for(total), 256, 0, (cudaStream_t)stream, Y, pos_of_pair, wts, (const __nv_bfloat16*)shared, T, d, top, out);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == kF32 && y_dtype == kF32) TTIE_LAUNCH((moe_combine_kernel<float, float>), grid_for(total), 256, 0, s, (const float*)Y, pos_of_pair, wts, (const float*)shared, T, d, top, out);
+    else if (y_dtype == kF32) TTIE_LAUNCH((moe_combine_kernel<__nv_bfloat16, float>), grid_for(total), 256, 0, s, (const float*)Y, pos_of_pair, wts, (const __nv_bfloat16*)shared, T, d, top, out);
+    else if (dtype == kBF16) TTIE_LAUNCH((moe_combine_kernel<__nv_bfloat16, __nv_bfloat16>), grid_for(total), 256, 0, s, (const __nv_bfloat16*)Y, pos_of_pair, wts, (const __nv_bfloat16*)shared, T, d, top, out);
+    else TTIE_FAIL("moe_combine: expert rows of dtype %d beside a shared expert of dtype %d", y_dtype, dtype);
     TTIE_CHECK_LAUNCH("moe_combine");
     return 0;
 }

@@ -27,10 +27,10 @@ __global__ void causal_conv_kernel(const T* __restrict__ in, long long ld, int c
                                    int state_rows, const int* __restrict__ token_seq, const int* __restrict__ qsl,
                                    const int* __restrict__ slot_ids, float* __restrict__ u32, T* __restrict__ u_c) {
     TTIE_PDL_ENTRY();
-    const size_t total = (size_t)T_ * width;
-    for (size_t e = blockIdx.x * (size_t)blockDim.x + threadIdx.x; e < total; e += (size_t)gridDim.x * blockDim.x) {
-        const int c = (int)(e % width);
-        const int t = (int)(e / width);
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;             // grid: (channels, tokens)
+    if (c >= width) return;
+    for (int t = blockIdx.y; t < T_; t += gridDim.y) {
+        const size_t e = (size_t)t * width + c;
         const int s = token_seq[t];
         const int j = t - qsl[s];                                   // index within the request's tokens of this step
         const float* tail = state + ((size_t)slot_row(slot_ids[s], state_rows) * taps + 1) * width;
@@ -51,14 +51,15 @@ struct ScanArgs {
     void* out; int T; int width; int taps; int bs; float decay_c; int num_seqs;
 };
 
+// (the pointers are passed as __restrict__ locals so that the loads of the next tokens may move above this token's store)
 template <typename T, typename W>
-__device__ __forceinline__ void gate_step(const ScanArgs& a, int t, int c, int blk, int o, float br, float bi, float sp,
-                                          float& av, float& bv) {
-    const float* g = a.pre + ((size_t)blk * a.T + t) * (2 * a.bs);
+__device__ __forceinline__ void gate_step(const ScanArgs& a, const float* __restrict__ pre, const float* __restrict__ u, int t, int c,
+                                          int blk, int o, float br, float bi, float sp, float& av, float& bv) {
+    const float* g = pre + ((size_t)blk * a.T + t) * (2 * a.bs);
     const float r = sigmoidf_(g[o] + br), i = sigmoidf_(g[a.bs + o] + bi);
     const float loga = -a.decay_c * r * sp;
     av = expf(loga);
-    bv = sqrtf(-expm1f(2.0f * loga)) * i * a.u[(size_t)t * a.width + c];
+    bv = sqrtf(-expm1f(2.0f * loga)) * i * u[(size_t)t * a.width + c];
 }
 
 template <typename T>
@@ -83,13 +84,16 @@ rglru_scan_kernel(ScanArgs a) {
     if (n <= 0) return;
     float* row = a.state + (size_t)slot_row(a.slot_ids[s], a.state_rows) * a.taps * a.width;
     const int blk = c / a.bs, o = c % a.bs;
+    const float* __restrict__ pre = a.pre;
+    const float* __restrict__ u = a.u;
     const float br = to_f32(((const W*)a.br)[c]), bi = to_f32(((const W*)a.bi)[c]), sp = softplusf_(to_f32(((const W*)a.lam)[c]));
-    const T* ypre = (const T*)a.ypre;
-    T* out = (T*)a.out;
+    const T* __restrict__ ypre = (const T*)a.ypre;
+    T* __restrict__ out = (T*)a.out;
     float S = row[c];
+#pragma unroll 4
     for (int t = q0; t < q0 + n; ++t) {
         float av, bv;
-        gate_step<T, W>(a, t, c, blk, o, br, bi, sp, av, bv);
+        gate_step<T, W>(a, pre, u, t, c, blk, o, br, bi, sp, av, bv);
         S = fmaf(av, S, bv);
         out[(size_t)t * a.width + c] = from_f32<T>(S * gelu_tanhf_(to_f32(ypre[(size_t)t * a.ld_y + a.col_y + c])));
     }
@@ -100,7 +104,7 @@ rglru_scan_kernel(ScanArgs a) {
 // ---- the chunked form.  Pass 1: per (chunk, channel) the recurrence over the chunk from S = 0: A = prod a, B = the state it
 // would reach.  Pass 2: per (request, channel) carry S over the chunk edges (S_edge <- A * S_edge + B), keeping the state at
 // every chunk's start.  Pass 3: per (chunk, channel) the recurrence again from the chunk's start state, writing the outputs.
-constexpr int CHUNK = 64;
+constexpr int CHUNK = 32;
 
 template <typename T, typename W>
 __global__ void __launch_bounds__(128)
@@ -112,11 +116,14 @@ rglru_chunk_reduce_kernel(ScanArgs a, const int* __restrict__ chunk_seq, const i
     if (s < 0) return;
     const int t0 = chunk_t0[k], t1 = min(t0 + CHUNK, a.qsl[s + 1]);
     const int blk = c / a.bs, o = c % a.bs;
+    const float* __restrict__ pre = a.pre;
+    const float* __restrict__ u = a.u;
     const float br = to_f32(((const W*)a.br)[c]), bi = to_f32(((const W*)a.bi)[c]), sp = softplusf_(to_f32(((const W*)a.lam)[c]));
     float A = 1.f, B = 0.f;
+#pragma unroll 4
     for (int t = t0; t < t1; ++t) {
         float av, bv;
-        gate_step<T, W>(a, t, c, blk, o, br, bi, sp, av, bv);
+        gate_step<T, W>(a, pre, u, t, c, blk, o, br, bi, sp, av, bv);
         A *= av;
         B = fmaf(av, B, bv);
     }
@@ -134,7 +141,15 @@ rglru_chunk_carry_kernel(ScanArgs a, const int* __restrict__ seq_chunk0, float2*
     float* row = a.state + (size_t)slot_row(a.slot_ids[s], a.state_rows) * a.taps * a.width;
     float S = row[c];
     const int k0 = seq_chunk0[s], nk = (n + CHUNK - 1) / CHUNK;
-    for (int k = k0; k < k0 + nk; ++k) {
+    int k = k0;
+    for (; k + 4 <= k0 + nk; k += 4) {                               // four chunks' pairs in flight: the chain is the fma, not the loads
+        float2 v[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) v[j] = ab[(size_t)(k + j) * a.width + c];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { ab[(size_t)(k + j) * a.width + c].x = S; S = fmaf(v[j].x, S, v[j].y); }
+    }
+    for (; k < k0 + nk; ++k) {
         const float2 v = ab[(size_t)k * a.width + c];
         ab[(size_t)k * a.width + c].x = S;                           // the state this chunk starts from
         S = fmaf(v.x, S, v.y);
@@ -153,13 +168,16 @@ rglru_chunk_apply_kernel(ScanArgs a, const int* __restrict__ chunk_seq, const in
     if (s < 0) return;
     const int t0 = chunk_t0[k], t1 = min(t0 + CHUNK, a.qsl[s + 1]);
     const int blk = c / a.bs, o = c % a.bs;
+    const float* __restrict__ pre = a.pre;
+    const float* __restrict__ u = a.u;
     const float br = to_f32(((const W*)a.br)[c]), bi = to_f32(((const W*)a.bi)[c]), sp = softplusf_(to_f32(((const W*)a.lam)[c]));
-    const T* ypre = (const T*)a.ypre;
-    T* out = (T*)a.out;
+    const T* __restrict__ ypre = (const T*)a.ypre;
+    T* __restrict__ out = (T*)a.out;
     float S = ab[(size_t)k * a.width + c].x;
+#pragma unroll 4
     for (int t = t0; t < t1; ++t) {
         float av, bv;
-        gate_step<T, W>(a, t, c, blk, o, br, bi, sp, av, bv);
+        gate_step<T, W>(a, pre, u, t, c, blk, o, br, bi, sp, av, bv);
         S = fmaf(av, S, bv);
         out[(size_t)t * a.width + c] = from_f32<T>(S * gelu_tanhf_(to_f32(ypre[(size_t)t * a.ld_y + a.col_y + c])));
     }
@@ -188,7 +206,7 @@ extern "C" int ttie_causal_conv(const void* in, long long ld, int col0, int T, i
     if (T <= 0) return 0;
     if (taps < 1) TTIE_FAIL("causal_conv: %d taps", taps);
     cudaStream_t s = (cudaStream_t)stream;
-    const int grid = grid_for((size_t)T * width);
+    const dim3 grid(ceil_div(width, 256), T < 65535 ? T : 65535);
 #define CC(TT, WW) TTIE_LAUNCH((causal_conv_kernel<TT, WW>), grid, 256, 0, s, (const TT*)in, ld, col0, T, width, taps, (const WW*)cw, \
                                (const WW*)cb, state, state_rows, token_seq, qsl, slot_ids, u32, (TT*)u_c)
     if (dtype == kF32) { if (w_dtype != kF32) TTIE_FAIL("causal_conv: a 32-bit run needs 32-bit weights"); CC(float, float); }

@@ -72,8 +72,9 @@ _SIGNATURES = {
     "ttie_moe_route": [_c_void, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_void, _c_void, _c_void],
     "ttie_moe_plan": [_c_void, _c_int, _c_int, _c_int, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void],
     "ttie_grouped_gemm": [_c_void, _c_ll, _c_void, _c_int, _c_void, _c_ll, _c_ll, _c_void, _c_ll, _c_void, _c_void, _c_int, _c_int, _c_int,
-                          _c_int, _c_int, _c_void],
-    "ttie_moe_combine": [_c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_void, _c_int, _c_void],
+                          _c_int, _c_int, _c_int, _c_void],
+    "ttie_gather_rows": [_c_void, _c_ll, _c_void, _c_int, _c_int, _c_int, _c_void, _c_int, _c_void],
+    "ttie_moe_combine": [_c_void, _c_int, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_void, _c_int, _c_void],
     "ttie_sample": [_c_void, _c_int, _c_int, _c_void, _c_void, _c_void, _c_void, _c_void],
     "ttie_sample_tuned": [_c_void, _c_int, _c_int, _c_void, _c_void, _c_void, _c_void, _c_int, _c_void],
 }
@@ -126,6 +127,7 @@ class CudaOps:
         self._swiglu_choice = {}                # (F, K, row bucket) -> True where the fused tcgen05 gate/up + SwiGLU kernel measured faster
         self._product_choice = {}               # (N, K, row bucket[, "split"]) -> "skinny" | "library" (tune_products; "split": for callers that take partial sums)
         self._skinny_tuned = {}                 # (N, K, row bucket 8 | 16) -> (K range per CTA, form code) where tune_products found a faster form
+        self._grouped_mm = None                 # the library's grouped product: None = not looked up yet, False = this build has none
         self.product_timings = {}               # what tune_products measured: (N, K, rows) -> {"library": ms, "skinny": ms (best form), "skinny_uncut": ms, ...}
         self.lib.ttie_attn_tc_supported.restype = _c_int
         if os.environ.get("TTIE_NVTX", "0") not in ("", "0"):
@@ -953,14 +955,46 @@ class CudaOps:
         self.launches += 1
         return plan
 
+    grouped_few_rows = 64                   # (token, choice) pairs up to which the grouped product streams every tile's weights once
+
+    def _library_grouped(self, x, w, plan, gather_div):
+        """The library's grouped product (bfloat16, many rows): rows gathered into expert order, then one call whose group
+        boundaries are read on the device.  None where it does not apply (sizes, or a build of the library without it)."""
+        if self._grouped_mm is False or x.dtype != torch.bfloat16 or w.shape[1] % 8 or w.shape[2] % 8:
+            return None
+        if self._grouped_mm is None:
+            self._grouped_mm = getattr(torch.nn.functional, "grouped_mm", None) or getattr(torch, "_grouped_mm", None) or False
+            if self._grouped_mm is False:
+                return None
+        rows = x
+        if gather_div:
+            rows = torch.empty((plan["pairs"], x.shape[1]), dtype=x.dtype, device=x.device)
+            self._check(self.lib.ttie_gather_rows(_ptr(x), x.stride(0), _ptr(plan["pair_of_pos"]), int(gather_div), plan["pairs"],
+                                                  x.shape[1], _ptr(rows), self._dt(x), self._stream(x)), "gather_rows")
+            self.launches += 1
+        try:
+            return self._grouped_mm(rows, w.transpose(1, 2), offs=plan["offsets"][1:])
+        except (RuntimeError, TypeError, NotImplementedError):
+            if torch.cuda.is_current_stream_capturing():
+                raise
+            self._grouped_mm = False                                    # this build has none for the device: the own kernel serves
+            return None
+
     def grouped_linear(self, x, w, plan, gather_div=0, out_dtype=None):
         """Rows sorted by expert times their expert's matrix: w [E, N, K]; row ``pos`` of the result is
-        x[pair_of_pos[pos] // gather_div] @ w[e].T (``gather_div`` 0: x[pos])."""
+        x[pair_of_pos[pos] // gather_div] @ w[e].T (``gather_div`` 0: x[pos]).  Few rows: a kernel that streams each tile's
+        weights once; many rows in bfloat16: the library's grouped product; else (float32) FFMA tiles."""
         E, N, K = w.shape
+        few = plan["pairs"] <= self.grouped_few_rows
+        if not few and x.dtype == torch.bfloat16:
+            out = self._library_grouped(x, w, plan, gather_div)
+            if out is not None:
+                return out
         out = torch.empty((plan["pairs"], N), dtype=out_dtype or x.dtype, device=x.device)
         self._check(self.lib.ttie_grouped_gemm(_ptr(x), x.stride(0), _ptr(plan["pair_of_pos"]) if gather_div else None, int(gather_div),
                                                _ptr(w), w.stride(0), w.stride(1), _ptr(out), N, _ptr(plan["tiles"]), _ptr(plan["meta"]),
-                                               plan["max_tiles"], N, K, self._dt(x), self._dt(out), self._stream(x)), "grouped_gemm")
+                                               plan["max_tiles"], N, K, self._dt(x), self._dt(out), 1 if few else 0, self._stream(x)),
+                    "grouped_gemm")
         self.launches += 1
         return out
 
@@ -968,8 +1002,9 @@ class CudaOps:
         """float32 [T, d]: the weighted sum of each token's expert rows (+ the shared expert's output)."""
         out = torch.empty((num_tokens, dim), dtype=torch.float32, device=y.device)
         top = wts.shape[1]
-        self._check(self.lib.ttie_moe_combine(_ptr(y), _ptr(plan["pos_of_pair"]), _ptr(wts), _ptr(shared), num_tokens, dim, top,
-                                              _ptr(out), self._dt(shared) if shared is not None else 0, self._stream(y)), "moe_combine")
+        sdt = self._dt(shared) if shared is not None else self._dt(y)
+        self._check(self.lib.ttie_moe_combine(_ptr(y), self._dt(y), _ptr(plan["pos_of_pair"]), _ptr(wts), _ptr(shared), num_tokens, dim,
+                                              top, _ptr(out), sdt, self._stream(y)), "moe_combine")
         self.launches += 1
         return out
 
