@@ -402,7 +402,9 @@ def run_design(args, pk):
             mc = ModelConfig.from_dict(cfg)
             page = 64
             pages = batch * (ctx // page + 4) + Tp // page + 8
-            ec = EngineConfig(dtype="bfloat16", device="cuda:0", use_cuda_graphs=True,
+            # (the prompt's step is replayed from a graph like the decode steps: a step of a hundred launches at these sizes is
+            # otherwise timed by the host's launches, not by the GPU)
+            ec = EngineConfig(dtype="bfloat16", device="cuda:0", use_cuda_graphs=True, step_graph_max_tokens=Tp,
                               cache=CacheConfig(block_size=page, num_gpu_blocks=pages),
                               sched=SchedulerConfig(max_num_seqs=batch + 1, max_num_batched_tokens=4096, cudagraph_batch_sizes=[batch]))
             eng = Engine(mc, random_tensors(mc, 0, store_dtype="bfloat16", device="cuda:0"), ec)
@@ -418,9 +420,11 @@ def run_design(args, pk):
 
             for _ in range(3):
                 prefill_once()
-            p_ms = timed(prefill_once, 3) / 3
+            p_ms = timed(prefill_once, 5) / 5
             window = 1024 if label == "munevik" else 0
+            saved_cap, eng.stepper.capture_repeated = eng.stepper.capture_repeated, False     # the recorded step runs eagerly
             p_ops = time_ops(eng, prefill_once, pk, [(Tp, Tp)], window)
+            eng.stepper.capture_repeated = saved_cap
             ms, end_len, launches = decode_kernel_path(eng, batch, ctx - (W + K), K, W, vocab, synthetic_fill=False)
             # one decode step, eagerly, for the per-operation times
             rids = [f"d{i}" for i in range(batch)]

@@ -52,3 +52,22 @@ MUN_D = {"architecture": "Munevik", "vocab": 200, "width": 128, "postln_alpha": 
     recurrent_layer(128, 2, 3, dense_mlp(160, 2.0)),
     attention_layer(8, 32, 16, 32, 112, 33, None, kv_from=0),
 ]}
+
+# cache rows of 256 values: every attention step takes the head-size-256 tensor-core kernel in bfloat16
+MUN_E = {"architecture": "Munevik", "vocab": 150, "width": 96, "postln_alpha": 2.0, "norm": {"eps": 1e-6}, "layers": [
+    attention_layer(4, 24, 24, 16, 232, 40, dense_mlp(64, 1.0)),
+    attention_layer(2, 24, 24, 40, 232, 77, None, kv_from=0),
+]}
+
+# sizes that are multiples of nothing: odd widths, a cache row of 137 values (padded to 144: the general attention kernel in
+# both dtypes), blocks of 10 channels, a vocabulary of 101
+MUN_F = {"architecture": "Munevik", "vocab": 101, "width": 50, "postln_alpha": 3.0, "norm": {"eps": 1e-5}, "layers": [
+    attention_layer(3, 10, 6, 7, 131, 11, moe_mlp(3, 3, 3, 2, 19, 1.3, shared=9), base=77.0),
+    recurrent_layer(50, 5, 3, dense_mlp(33, 0.7)),
+]}
+
+# recurrent layers only (no pages at all), and attention layers only (each with a cache of its own)
+MUN_G = {"architecture": "Munevik", "vocab": 80, "width": 32, "postln_alpha": 1.0, "norm": {"eps": 1e-6}, "layers": [
+    recurrent_layer(32, 2, 3, dense_mlp(48, 2.0)), recurrent_layer(64, 64, 2, None)]}
+MUN_H = {"architecture": "Munevik", "vocab": 80, "width": 32, "postln_alpha": 1.0, "norm": {"eps": 1e-6}, "layers": [
+    attention_layer(2, 8, 8, 8, 24, 16, None), attention_layer(4, 4, 4, 12, 12, 3, dense_mlp(48, 2.0))]}

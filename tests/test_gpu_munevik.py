@@ -13,12 +13,12 @@ from tiny_transformer_inference_engine_b200.parts.base import PartSpec, StepCont
 from tiny_transformer_inference_engine_b200.registry import build_part
 from tiny_transformer_inference_engine_b200.weights import random_tensors
 
-from munevik_configs import MUN_A, MUN_B, MUN_C, MUN_D, attention_layer, recurrent_layer, moe_mlp, dense_mlp
+from munevik_configs import MUN_A, MUN_B, MUN_C, MUN_D, MUN_E, MUN_F, MUN_G, MUN_H
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
-CONFIGS = {"A": MUN_A, "B": MUN_B, "C": MUN_C, "D": MUN_D}
+CONFIGS = {"A": MUN_A, "B": MUN_B, "C": MUN_C, "D": MUN_D, "E": MUN_E, "F": MUN_F, "G": MUN_G, "H": MUN_H}
 
 
 @pytest.fixture(scope="module")
@@ -75,13 +75,13 @@ def check(got, exp, dtype):
 
 # ------------------------------------------------------------------------------------------ the whole model, four cuts
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E", "F", "G", "H"])
 def test_schedules_against_plain_model(name, dtype):
     cfg = CONFIGS[name]
     w = weights_for(cfg, 5 + ord(name))
     reqs = requests(cfg, [1, 2, 37, 70, 101, 23], seed=3)
     exp = expected_for(cfg, w, reqs, dtype)
-    page = {"A": 16, "B": 8, "C": 4, "D": 32}[name]
+    page = {"A": 16, "B": 8, "C": 4, "D": 32, "E": 16, "F": 8, "G": 16, "H": 2}[name]
     for cut in (tu.whole, tu.prefill_then_decode, tu.portions, tu.mixed):
         steps = cut(reqs)
         tokens = tu.max_live_tokens(steps, rounding=page)
@@ -128,6 +128,28 @@ def test_greedy_generation_through_the_scheduler(graphs):
     assert got == want
 
 
+def test_repeated_portions_replayed_from_graphs():
+    """Steps of one layout (a 40-token prompt: more (token, expert) pairs than the few-rows kernel takes, so the grouped
+    products are the many-rows forms) are captured the second time and replayed after that; all three must give the plain
+    model's logits, in both dtypes."""
+    cfg = dict(MUN_A, max_seq_len=128)
+    for dtype in ("float32", "bfloat16"):
+        w = weights_for(cfg, 41)
+        reqs = requests(cfg, [40, 40, 40, 40], seed=6)
+        exp = expected_for(cfg, w, reqs, dtype)
+        eng = engine_for(cfg, w, dtype, pages=16, max_seqs=2, budget=64, graphs=True)
+        got = {}
+        for rid, toks in reqs.items():
+            eng.manager.admit(rid)
+            eng.manager.extend(rid, 0, 40)
+            logits = eng.stepper.step([StepEntry(rid, 0, toks, list(range(40)))]).float().cpu()
+            for i in range(40):
+                got[(rid, i)] = logits[i].clone()
+            eng.manager.release(rid)
+        assert eng.stepper.counters["step_graphs_captured"] == 1 and eng.stepper.counters["step_graph_replays"] == 2
+        check(got, exp, dtype)
+
+
 # ------------------------------------------------------------------------------------------ each mechanism alone
 def ctx_for(ops, dtype, seqs, tables, slots=None):
     pos = [s + i for s, n in seqs for i in range(n)]
@@ -164,10 +186,11 @@ def part_with_weights(category, spec, dtype, ops, seed, scale=0.15):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_scaled_add_layernorm(ops, dtype):
-    part, w = part_with_weights("norm", PartSpec("layernorm", "n", {"dim": 200, "eps": 3e-4, "names": {"weight": "g", "bias": "g.b"}}),
+@pytest.mark.parametrize("dim", [200, 50, 8300])                         # the kernel's three forms: vectors of four, any width, wide rows
+def test_scaled_add_layernorm(ops, dtype, dim):
+    part, w = part_with_weights("norm", PartSpec("layernorm", "n", {"dim": dim, "eps": 3e-4, "names": {"weight": "g", "bias": "g.b"}}),
                                 dtype, ops, 0, scale=0.5)
-    x, delta = torch.randn(7, 200) * 3 + 1, torch.randn(7, 200).to(DT[dtype])
+    x, delta = torch.randn(7, dim) * 3 + 1, torch.randn(7, dim).to(DT[dtype])
     r = x.clone().to(DEV)
     out = part.scale_add_norm(r, delta.to(DEV), 1.7)
     exp = pm.layer_norm(1.7 * x.double() + delta.double(), w["n.g"], w["n.g.b"], 3e-4)
@@ -175,7 +198,7 @@ def test_scaled_add_layernorm(ops, dtype):
     assert rel(out.float(), exp) < (1e-5 if dtype == "float32" else 8e-3)
     # partial sums of a split product as the delta; rows gathered without touching the stream
     r2 = x.clone().to(DEV)
-    parts = torch.randn(3, 7, 200)
+    parts = torch.randn(3, 7, dim)
     part.scale_add_norm(r2, parts.to(DEV), 0.5)
     assert rel(r2, pm.layer_norm(0.5 * x.double() + parts.double().sum(0), w["n.g"], w["n.g.b"], 3e-4)) < 1e-5
     rows = torch.tensor([4, 0, 6], dtype=torch.int32, device=DEV)

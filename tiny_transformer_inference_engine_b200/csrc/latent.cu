@@ -82,6 +82,58 @@ __global__ void gate_heads_kernel(const T* __restrict__ v, const T* __restrict__
     }
 }
 
+// ---- bfloat16, eight values per thread (every size a multiple of 8, rows 16-byte aligned)
+__device__ __forceinline__ uint4 scale8(const uint4 v, float g) {
+    uint4 o;
+    const __nv_bfloat162* a = reinterpret_cast<const __nv_bfloat162*>(&v);
+    __nv_bfloat162* b = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(a[i]); b[i] = __floats2bfloat162_rn(f.x * g, f.y * g); }
+    return o;
+}
+
+__global__ void latent_query_vec8_kernel(const __nv_bfloat16* __restrict__ q, long long ld, const __nv_bfloat16* __restrict__ folded, int T_,
+                                         int H, int dim, int rank, int rot, int width, const float2* __restrict__ cs,
+                                         __nv_bfloat16* __restrict__ out) {
+    TTIE_PDL_ENTRY();
+    const int half = rot >> 1, per_row = H * width;
+    const int col = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+    if (col >= per_row) return;
+    const int h = col / width, i = col - h * width;
+    for (size_t t = blockIdx.y; t < (size_t)T_; t += gridDim.y) {
+        uint4 o = make_uint4(0u, 0u, 0u, 0u);
+        if (i < rank) {
+            o = *reinterpret_cast<const uint4*>(folded + ((size_t)h * T_ + t) * rank + i);
+        } else if (i < rank + rot) {
+            const int k = i - rank;
+            const uint4 v = *reinterpret_cast<const uint4*>(q + t * ld + (size_t)h * (dim + rot) + dim + k);
+            const __nv_bfloat162* a = reinterpret_cast<const __nv_bfloat162*>(&v);
+            __nv_bfloat162* b = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+            for (int p = 0; p < 4; ++p) {
+                const float2 c = cs[t * half + (k >> 1) + p];
+                const float2 f = __bfloat1622float2(a[p]);
+                b[p] = __floats2bfloat162_rn(f.x * c.x - f.y * c.y, f.y * c.x + f.x * c.y);
+            }
+        }
+        *reinterpret_cast<uint4*>(out + t * per_row + col) = o;
+    }
+}
+
+__global__ void gate_heads_vec8_kernel(const __nv_bfloat16* __restrict__ v, const __nv_bfloat16* __restrict__ gate, long long ld, int T_, int H,
+                                       int vdim, __nv_bfloat16* __restrict__ out) {
+    TTIE_PDL_ENTRY();
+    const int per_row = H * vdim;
+    const int col = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+    if (col >= per_row) return;
+    const int h = col / vdim, j = col - h * vdim;
+    for (size_t t = blockIdx.y; t < (size_t)T_; t += gridDim.y) {
+        const float g = 1.0f / (1.0f + expf(-__bfloat162float(gate[t * ld + h])));
+        *reinterpret_cast<uint4*>(out + t * per_row + col) = scale8(*reinterpret_cast<const uint4*>(v + ((size_t)h * T_ + t) * vdim + j), g);
+    }
+}
+
+inline bool aligned16(const void* p) { return (((uintptr_t)p) & 15) == 0; }
 inline int grid_for(size_t total) { return (int)((total + 255) / 256 < 8192 ? (total + 255) / 256 : 8192); }
 }  // namespace
 
@@ -106,6 +158,13 @@ extern "C" int ttie_latent_query(const void* q, long long ld, const void* folded
                                  const void* cs, void* out, int dtype, void* stream) {
     if (T <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == kBF16 && rank % 8 == 0 && rot % 8 == 0 && dim % 8 == 0 && width % 8 == 0 && ld % 8 == 0 && aligned16(q) && aligned16(folded) && aligned16(out)) {
+        const dim3 g8(ceil_div(H * width / 8, 128), T < 65535 ? T : 65535);
+        TTIE_LAUNCH(latent_query_vec8_kernel, g8, 128, 0, s, (const __nv_bfloat16*)q, ld, (const __nv_bfloat16*)folded, T, H, dim, rank, rot, width,
+                    (const float2*)cs, (__nv_bfloat16*)out);
+        TTIE_CHECK_LAUNCH("latent_query");
+        return 0;
+    }
     const dim3 grid(ceil_div(H * width, 256), T < 65535 ? T : 65535);
     if (dtype == kF32) TTIE_LAUNCH(latent_query_kernel<float>, grid, 256, 0, s, (const float*)q, ld, (const float*)folded, T, H, dim, rank, rot, width, (const float2*)cs, (float*)out);
     else TTIE_LAUNCH(latent_query_kernel<__nv_bfloat16>, grid, 256, 0, s, (const __nv_bfloat16*)q, ld, (const __nv_bfloat16*)folded, T, H, dim, rank, rot, width, (const float2*)cs, (__nv_bfloat16*)out);
@@ -116,6 +175,12 @@ extern "C" int ttie_latent_query(const void* q, long long ld, const void* folded
 extern "C" int ttie_gate_heads(const void* v, const void* gate, long long ld, int T, int H, int vdim, void* out, int dtype, void* stream) {
     if (T <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == kBF16 && vdim % 8 == 0 && aligned16(v) && aligned16(out)) {
+        const dim3 g8(ceil_div(H * vdim / 8, 128), T < 65535 ? T : 65535);
+        TTIE_LAUNCH(gate_heads_vec8_kernel, g8, 128, 0, s, (const __nv_bfloat16*)v, (const __nv_bfloat16*)gate, ld, T, H, vdim, (__nv_bfloat16*)out);
+        TTIE_CHECK_LAUNCH("gate_heads");
+        return 0;
+    }
     const dim3 grid(ceil_div(H * vdim, 256), T < 65535 ? T : 65535);
     if (dtype == kF32) TTIE_LAUNCH(gate_heads_kernel<float>, grid, 256, 0, s, (const float*)v, (const float*)gate, ld, T, H, vdim, (float*)out);
     else TTIE_LAUNCH(gate_heads_kernel<__nv_bfloat16>, grid, 256, 0, s, (const __nv_bfloat16*)v, (const __nv_bfloat16*)gate, ld, T, H, vdim, (__nv_bfloat16*)out);

@@ -92,6 +92,76 @@ scale_add_layernorm_reg_kernel(float* __restrict__ resid, const T* __restrict__ 
     }
 }
 
+// Four values per load (d a multiple of 4): two such vectors per thread.
+__device__ __forceinline__ float4 ld4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 ld4(const __nv_bfloat16* p) {
+    const uint2 v = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.x)), b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ void st4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void st4(__nv_bfloat16* p, float4 v) {
+    uint2 o;
+    *reinterpret_cast<__nv_bfloat162*>(&o.x) = __floats2bfloat162_rn(v.x, v.y);
+    *reinterpret_cast<__nv_bfloat162*>(&o.y) = __floats2bfloat162_rn(v.z, v.w);
+    *reinterpret_cast<uint2*>(p) = o;
+}
+
+template <typename T, typename W>
+__global__ void __launch_bounds__(1024)
+scale_add_layernorm_vec_kernel(float* __restrict__ resid, const T* __restrict__ delta, const float* __restrict__ dpart, int S,
+                               long long part_stride, const int* __restrict__ rows, const W* __restrict__ weight,
+                               const W* __restrict__ bias, T* __restrict__ out, float* __restrict__ out32, int d, float alpha, float eps,
+                               int write_resid) {
+    constexpr int PER = 2;
+    __shared__ float scratch[32];
+    TTIE_PDL_ENTRY();
+    const int r = blockIdx.x;
+    const size_t src = rows ? (size_t)rows[r] : (size_t)r;
+    float* x = resid + src * d;
+    float4 v[PER], w[PER], b[PER];
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+        const int i = (threadIdx.x + j * blockDim.x) * 4;
+        v[j] = w[j] = b[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (i < d) {
+            const float4 xv = ld4(x + i);
+            v[j] = make_float4(alpha * xv.x, alpha * xv.y, alpha * xv.z, alpha * xv.w);
+            if (delta) { const float4 dv = ld4(delta + src * d + i); v[j].x += dv.x; v[j].y += dv.y; v[j].z += dv.z; v[j].w += dv.w; }
+            w[j] = ld4(weight + i);
+            if (bias) b[j] = ld4(bias + i);
+        }
+    }
+    for (int s = 0; s < S; ++s)
+#pragma unroll
+        for (int j = 0; j < PER; ++j) {
+            const int i = (threadIdx.x + j * blockDim.x) * 4;
+            if (i < d) { const float4 p = ld4(dpart + (size_t)s * part_stride + src * d + i); v[j].x += p.x; v[j].y += p.y; v[j].z += p.z; v[j].w += p.w; }
+        }
+    float sum = 0.f;
+#pragma unroll
+    for (int j = 0; j < PER; ++j) sum += (v[j].x + v[j].y) + (v[j].z + v[j].w);
+    const float mean = block_sum(sum, scratch) / (float)d;
+    float sq = 0.f;
+#pragma unroll
+    for (int j = 0; j < PER; ++j)
+        if ((threadIdx.x + j * blockDim.x) * 4 < d) {
+            const float a0 = v[j].x - mean, a1 = v[j].y - mean, a2 = v[j].z - mean, a3 = v[j].w - mean;
+            sq += (a0 * a0 + a1 * a1) + (a2 * a2 + a3 * a3);
+        }
+    const float rstd = 1.0f / sqrtf(block_sum(sq, scratch) / (float)d + eps);
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+        const int i = (threadIdx.x + j * blockDim.x) * 4;
+        if (i >= d) continue;
+        const float4 y = make_float4((v[j].x - mean) * rstd * w[j].x + b[j].x, (v[j].y - mean) * rstd * w[j].y + b[j].y,
+                                     (v[j].z - mean) * rstd * w[j].z + b[j].z, (v[j].w - mean) * rstd * w[j].w + b[j].w);
+        if (write_resid) st4(x + i, y);
+        if (out) st4(out + (size_t)r * d + i, y);
+        if (out32) st4(out32 + (size_t)r * d + i, y);
+    }
+}
+
 template <typename T>
 __global__ void cast_rows_kernel(const float* __restrict__ in, T* __restrict__ out, size_t n) {
     TTIE_PDL_ENTRY();
@@ -101,6 +171,14 @@ __global__ void cast_rows_kernel(const float* __restrict__ in, T* __restrict__ o
 template <typename T, typename W>
 int launch_ln(float* resid, const void* delta, const float* dpart, int S, long long part_stride, const int* rows, const void* w,
               const void* b, void* out, float* out32, int R, int d, float alpha, float eps, int write_resid, cudaStream_t s) {
+    const uintptr_t all = (uintptr_t)resid | (uintptr_t)delta | (uintptr_t)dpart | (uintptr_t)w | (uintptr_t)b | (uintptr_t)out | (uintptr_t)out32;
+    if (d % 4 == 0 && d <= 8 * 1024 && (all & 15) == 0 && part_stride % 4 == 0) {
+        const int threads = ((d / 8 + 31) / 32) * 32 < 32 ? 32 : ((d / 8 + 31) / 32) * 32;
+        TTIE_LAUNCH((scale_add_layernorm_vec_kernel<T, W>), R, threads, 0, s, resid, (const T*)delta, dpart, S, part_stride, rows,
+                    (const W*)w, (const W*)b, (T*)out, out32, d, alpha, eps, write_resid);
+        TTIE_CHECK_LAUNCH("scale_add_layernorm");
+        return 0;
+    }
     if (d <= 8 * 1024) {
         const int threads = d <= 1024 ? 128 : d <= 2048 ? 256 : d <= 4096 ? 512 : 1024;
         TTIE_LAUNCH((scale_add_layernorm_reg_kernel<T, W, 8>), R, threads, 0, s, resid, (const T*)delta, dpart, S, part_stride, rows,

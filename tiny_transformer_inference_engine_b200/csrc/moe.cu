@@ -1,10 +1,10 @@
 // Gated linear units with their constants as parameters, and a routed mixture of experts.
 //   glu:            y = g' * sigmoid(alpha * g') * (u' + shift), g' = min(g, limit), u' = clamp(u, -limit, limit) (limit <= 0:
 //                   no clamp); alpha = 1, shift = 0 is SwiGLU.  32-bit arithmetic, rounded once.
-//   moe_route:      scores s = sigmoid(z) from 32-bit router logits; experts form equal groups
-//                   of neighbours, a group's score is the sum of its `group_top` largest scores, only experts of the best
-//                   `keep` groups can be chosen; the `top` largest scores among those win (ties: the lower index); weights are
-//                   s * scale, optionally renormalised to sum to `scale`.  One thread per token, all 32-bit.
+//   moe_route:      scores s = sigmoid(z) from 32-bit router logits; expert e is in group
+//                   e / (E / groups); a group is rated by adding up its `group_top` highest scores, the `keep` best-rated
+//                   groups stay eligible; the `top` highest scores among eligible experts are taken (ties: the lower index),
+//                   weighted s * scale, optionally renormalised to sum to `scale`.  One thread per token, all 32-bit.
 //   moe_plan:       counting sort of the (token, choice) pairs by expert, on the device: offsets per expert, position of each
 //                   pair, and a table of row tiles (expert, first row, rows) for the grouped product; nothing is read on the host.
 //   grouped_gemm:   C[pos, :] = A[row_of(pos), :] * W[expert_of_tile]^T for every tile of the table (FFMA, 32-bit accumulation,
@@ -290,6 +290,36 @@ __global__ void moe_combine_kernel(const TY* __restrict__ Y, const int* __restri
     }
 }
 
+// bfloat16 expert rows and shared rows, eight values per thread (d a multiple of 8)
+__global__ void moe_combine_vec8_kernel(const __nv_bfloat16* __restrict__ Y, const int* __restrict__ pos_of_pair, const float* __restrict__ wts,
+                                        const __nv_bfloat16* __restrict__ shared, int T_, int d8, int top, float* __restrict__ out) {
+    TTIE_PDL_ENTRY();
+    const size_t total = (size_t)T_ * d8;
+    for (size_t e = blockIdx.x * (size_t)blockDim.x + threadIdx.x; e < total; e += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = e / d8;
+        const int i = (int)(e % d8) * 8;
+        float acc[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+        for (int k = 0; k < top; ++k) {
+            const float w = wts[t * top + k];
+            const uint4 v = *reinterpret_cast<const uint4*>(Y + (size_t)pos_of_pair[t * top + k] * d8 * 8 + i);
+            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(h[j]); acc[2 * j] = fmaf(w, f.x, acc[2 * j]); acc[2 * j + 1] = fmaf(w, f.y, acc[2 * j + 1]); }
+        }
+        if (shared) {
+            const uint4 v = *reinterpret_cast<const uint4*>(shared + t * d8 * 8 + i);
+            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(h[j]); acc[2 * j] += f.x; acc[2 * j + 1] += f.y; }
+        }
+        float* o = out + t * d8 * 8 + i;
+        *reinterpret_cast<float4*>(o) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+        *reinterpret_cast<float4*>(o + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
+    }
+}
+
 inline int grid_for(size_t total) { return (int)((total + 255) / 256 < 8192 ? (total + 255) / 256 : 8192); }
 }  // namespace
 
@@ -381,6 +411,11 @@ extern "C" int ttie_moe_combine(const void* Y, int y_dtype, const int* pos_of_pa
     if (T <= 0) return 0;
     const size_t total = (size_t)T * d;
     cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == kBF16 && y_dtype == kBF16 && d % 8 == 0 && ((((uintptr_t)Y) | ((uintptr_t)shared) | ((uintptr_t)out)) & 15) == 0) {
+        TTIE_LAUNCH(moe_combine_vec8_kernel, grid_for(total / 8), 256, 0, s, (const __nv_bfloat16*)Y, pos_of_pair, wts, (const __nv_bfloat16*)shared, T, d / 8, top, out);
+        TTIE_CHECK_LAUNCH("moe_combine");
+        return 0;
+    }
     if (dtype == kF32 && y_dtype == kF32) TTIE_LAUNCH((moe_combine_kernel<float, float>), grid_for(total), 256, 0, s, (const float*)Y, pos_of_pair, wts, (const float*)shared, T, d, top, out);
     else if (y_dtype == kF32) TTIE_LAUNCH((moe_combine_kernel<__nv_bfloat16, float>), grid_for(total), 256, 0, s, (const float*)Y, pos_of_pair, wts, (const __nv_bfloat16*)shared, T, d, top, out);
     else if (dtype == kBF16) TTIE_LAUNCH((moe_combine_kernel<__nv_bfloat16, __nv_bfloat16>), grid_for(total), 256, 0, s, (const __nv_bfloat16*)Y, pos_of_pair, wts, (const __nv_bfloat16*)shared, T, d, top, out);

@@ -1,7 +1,7 @@
 """The Munevik design as data: a post-norm decoder of latent-attention and recurrent layers.
 
-Token embedding; per layer ``x <- norm1(alpha * x + mixer(x))`` and, where the layer has a feed-forward,
-``x <- norm2(alpha * x + ff(x))`` with LayerNorm (weight and bias); the model's LayerNorm; logits from the embedding table.
+Token embedding; post-norm layers (``x = LN(alpha * x + sublayer(x))`` for the mixer and, where the layer has one, for the
+feed-forward; LayerNorm with weight and bias); the model's LayerNorm; logits from the embedding table.
 The mixer is latent attention (sliding window, gated heads, rotated key part shared by all heads; a layer may read an
 earlier layer's latent cache instead of keeping one) or the RG-LRU recurrent block; the feed-forward is a clamped gated
 linear unit or a grouped top-k mixture of SwiGLU experts with a shared expert.  Tensor names: ``embed``,

@@ -887,7 +887,8 @@ class CudaOps:
 
     # ---- recurrent block
     def causal_conv(self, xin, col0, width, taps, conv_w, conv_b, state, token_seq, query_start_loc, slot_ids, want_copy):
-        """Per-channel causal convolution over the step's tokens; inputs before the step come from the state rows.
+        """Per-channel causal convolution over the step's tokens (``conv_w`` tap-major [taps, width]); inputs before the
+        step come from the state rows.
         Returns (u float32 [T, width], u in the compute dtype or None)."""
         T = xin.shape[0]
         u32 = torch.empty((T, width), dtype=torch.float32, device=xin.device)
@@ -910,7 +911,7 @@ class CudaOps:
         if max_q_len > 2 * chunk:
             max_chunks = num_tokens // chunk + num_seqs
             ws = torch.empty(2 * max_chunks + num_seqs, dtype=torch.int32, device=xin.device)
-            ab = torch.empty((max_chunks, width, 2), dtype=torch.float32, device=xin.device)
+            ab = torch.empty((max_chunks, width, 3), dtype=torch.float32, device=xin.device)   # (prod a, input) per chunk, then the chunks' start states
         self._check(self.lib.ttie_rglru_scan(_ptr(pre), _ptr(gate_bias_r), _ptr(gate_bias_i), _ptr(lam), self._dt(lam), _ptr(u32),
                                              _ptr(xin), xin.stride(0), int(col_x), _ptr(ypre), ypre.stride(0), int(col_y),
                                              _ptr(state), state.shape[0], _ptr(query_start_loc), _ptr(slot_ids), num_seqs,
@@ -983,7 +984,8 @@ class CudaOps:
     def grouped_linear(self, x, w, plan, gather_div=0, out_dtype=None):
         """Rows sorted by expert times their expert's matrix: w [E, N, K]; row ``pos`` of the result is
         x[pair_of_pos[pos] // gather_div] @ w[e].T (``gather_div`` 0: x[pos]).  Few rows: a kernel that streams each tile's
-        weights once; many rows in bfloat16: the library's grouped product; else (float32) FFMA tiles."""
+        weights once; many rows in bfloat16: the library's grouped product (its result is bfloat16 whatever ``out_dtype``
+        asks: it has no wider output); else (float32) FFMA tiles."""
         E, N, K = w.shape
         few = plan["pairs"] <= self.grouped_few_rows
         if not few and x.dtype == torch.bfloat16:

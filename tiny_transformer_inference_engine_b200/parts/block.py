@@ -35,8 +35,8 @@ class PreNormBlock(Block):
 
 @register_part("block", "post_norm")
 class PostNormBlock(Block):
-    """Norm after the sum: ``x <- norm1(alpha * x + mixer(x))``, then ``x <- norm2(alpha * x + ffn(x))``; the sub-layers
-    read ``x`` itself.  The stream holds ``x`` in 32-bit; each norm kernel forms the scaled sum, normalises, rewrites the
+    """Post-norm: ``x = LN_a(alpha * x + mixer(x))`` followed by ``x = LN_b(alpha * x + ffn(x))``; each sub-layer's input is
+    the (already normalised) stream, not a normed copy of it.  The stream holds ``x`` in 32-bit; each norm kernel forms the scaled sum, normalises, rewrites the
     stream and hands the next sub-layer a copy in the compute dtype.  A layer without a feed-forward (``ffn`` None) ends
     after the first norm."""
 

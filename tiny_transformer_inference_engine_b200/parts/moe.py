@@ -1,9 +1,9 @@
 """A routed mixture of gated-linear-unit experts with grouped top-k selection and an optional shared expert.
 
-Router: ``z = W_r h`` in 32-bit (``h`` in the compute dtype), scores ``s = sigmoid(z)``.  The experts form ``groups`` equal
-groups of neighbours; a group's score is the sum of its ``group_top`` largest scores, and only experts of the best
-``keep`` groups can be chosen.  Of those the ``top`` largest scores win; their weights are ``s * scale`` (``renorm``:
-divided by their sum first).  The output is the weighted sum of the chosen experts' outputs plus, if there is one, a shared
+Router: ``z = W_r h`` in 32-bit (``h`` in the compute dtype), scores ``s = sigmoid(z)``.  Expert ``e`` belongs to group
+``e // (experts / groups)``.  Each group is rated by adding up its ``group_top`` highest scores; the ``keep`` best-rated groups
+stay eligible and the experts of all other groups are masked out.  Among the eligible experts the ``top`` highest scores are
+taken, each weighted ``s * scale`` (``renorm``: divided by the sum of the taken scores first).  The output is the weighted sum of the chosen experts' outputs plus, if there is one, a shared
 expert that every token runs.  An expert is ``down(act(gate h) * up h)`` with the activation's constants as parameters.
 
 On the device, with nothing read on the host (so a step can be captured in a graph): route -> counting sort of the

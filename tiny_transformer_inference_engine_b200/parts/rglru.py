@@ -1,11 +1,12 @@
 """The recurrent block with a real-gated linear recurrent unit (RG-LRU), as in the Griffin architecture.
 
 Two branches of size ``width`` from the block's input ``h``: ``y = gelu_tanh(W_y h + b_y)`` and
-``u = conv(W_x h + b_x)``, a causal per-channel convolution of ``taps`` taps (the last tap is the current token's; zeros
-before the start of the sequence).  ``u`` is cut into ``blocks`` equal parts; in part ``b`` the recurrence gate is
-``r = sigmoid(A_b u_b + a_b)`` and the input gate ``i = sigmoid(I_b u_b + i_b)`` (square matrices).  Then
-``log a = -decay * r * softplus(lam)``, ``a = exp(log a)``, ``S_t = a S_{t-1} + sqrt(1 - a^2) * i * u`` from ``S = 0`` (the
-first token is no special case), and the block returns ``W_o (S * y)``.
+``u = conv(W_x h + b_x)``, a short convolution along time with ``taps`` weights per channel: weight ``taps - 1`` multiplies
+the current token's input, weight ``k`` the input ``taps - 1 - k`` tokens back, and a new sequence has only zeros behind it.
+The channels of ``u`` fall into ``blocks`` consecutive slices of equal size; slice ``b`` has two square matrices that give its
+gates, ``r_t = sigmoid(A_b u_b + a_b)`` (recurrence) and ``i_t = sigmoid(I_b u_b + i_b)`` (input).  With
+``a_t = exp(-decay * softplus(lam) * r_t)`` the state moves as ``S_t = a_t * S_{t-1} + sqrt(1 - a_t^2) * (i_t * u_t)``; a new
+sequence has ``S = 0`` and its first token runs this same update.  The block returns ``W_o (S * y)``.
 
 Per request the state slot holds ``[taps, width]`` 32-bit values: the recurrent state and the convolution's last
 ``taps - 1`` inputs, so a sequence may be cut into steps anywhere.  Gates, decay and the recurrence are 32-bit in every
@@ -53,7 +54,7 @@ class RGLRU(Mixer):
         self.w_in = torch.cat([params[n["y"]], params[n["x"]]], dim=0).contiguous()             # [2W, d]: y first
         self.b_in = torch.cat([params[n["y_bias"]], params[n["x_bias"]]], dim=0).contiguous()
         vec = params[n["lam"]].dtype
-        self.conv_w = params[n["conv"]].to(vec).contiguous()
+        self.conv_w = params[n["conv"]].to(vec).t().contiguous()                               # tap-major [taps, W]: a tap's weights lie side by side
         self.conv_b = params[n["conv_bias"]].to(vec).contiguous()
         self.w_gates = torch.cat([params[n["gate_a"]], params[n["gate_i"]]], dim=1).contiguous()   # [B, 2*bs, bs]: r rows, then i rows
         self.gate_a_bias = params[n["gate_a_bias"]].to(vec).reshape(-1).contiguous()
