@@ -4,7 +4,7 @@
 //   moe_route:      scores s = sigmoid(z) from 32-bit router logits; expert e is in group
 //                   e / (E / groups); a group is rated by adding up its `group_top` highest scores, the `keep` best-rated
 //                   groups stay eligible; the `top` highest scores among eligible experts are taken (ties: the lower index),
-//                   weighted s * scale, optionally renormalised to sum to `scale`.  One thread per token, all 32-bit.
+//                   weighted s * scale, optionally renormalised to sum to `scale`.  One warp per token, all 32-bit.
 //   moe_plan:       counting sort of the (token, choice) pairs by expert, on the device: offsets per expert, position of each
 //                   pair, and a table of row tiles (expert, first row, rows) for the grouped product; nothing is read on the host.
 //   grouped_gemm:   C[pos, :] = A[row_of(pos), :] * W[expert_of_tile]^T for every tile of the table (FFMA, 32-bit accumulation,
@@ -56,51 +56,56 @@ __global__ void glu_vec8_kernel(const __nv_bfloat16* __restrict__ gu, long long 
 
 constexpr int MAX_EXPERTS = 512;
 
-__global__ void moe_route_kernel(const float* __restrict__ logits, int T_, int E, int groups, int keep, int group_top, int top,
-                                 float scale, int renorm, int* __restrict__ idx, float* __restrict__ wts) {
-    extern __shared__ float sm[];                                   // [blockDim.x][E] scores, then [blockDim.x][groups]
+// One warp per token: the lanes share the experts (scores), the groups (ratings and ranks) and the search for the next
+// largest score (a shuffle reduction per choice).  Shared memory per warp: E scores, then the groups' ratings and keep flags.
+constexpr int ROUTE_WARPS = 4;
+__global__ void __launch_bounds__(ROUTE_WARPS * 32)
+moe_route_kernel(const float* __restrict__ logits, int T_, int E, int groups, int keep, int group_top, int top,
+                 float scale, int renorm, int* __restrict__ idx, float* __restrict__ wts) {
+    extern __shared__ float sm[];
     TTIE_PDL_ENTRY();
-    const int t = blockIdx.x * blockDim.x + threadIdx.x;
-    if (t >= T_) return;
-    float* s = sm + (size_t)threadIdx.x * (E + groups);
-    float* gs = s + E;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * ROUTE_WARPS + warp;
+    if (t >= T_) return;                                             // (whole warps leave; nothing below synchronises the block)
+    float* s = sm + (size_t)warp * (E + 2 * groups);
+    float* rating = s + E;
+    float* kept = rating + groups;
     const int per = E / groups;
-    for (int e = 0; e < E; ++e) s[e] = 1.0f / (1.0f + expf(-logits[(size_t)t * E + e]));
-    // group scores: the sum of the group's `group_top` largest scores
-    for (int g = 0; g < groups; ++g) {
-        float acc = 0.f;
-        int taken0 = -1, taken1 = -1;                                // (group_top is at most 2 here; more: see the host check)
-        for (int k = 0; k < group_top && k < per; ++k) {
-            int best = -1;
-            for (int e = 0; e < per; ++e) {
-                if (e == taken0 || e == taken1) continue;
-                if (best < 0 || s[g * per + e] > s[g * per + best]) best = e;
-            }
-            acc += s[g * per + best];
-            if (k == 0) taken0 = best; else taken1 = best;
+    for (int e = lane; e < E; e += 32) s[e] = 1.0f / (1.0f + expf(-logits[(size_t)t * E + e]));
+    __syncwarp();
+    for (int g = lane; g < groups; g += 32) {                        // a group's rating: the sum of its `group_top` (1 or 2) highest scores
+        float b0 = -1.f, b1 = -1.f;
+        for (int e = 0; e < per; ++e) {
+            const float v = s[g * per + e];
+            if (v > b0) { b1 = b0; b0 = v; } else if (v > b1) b1 = v;
         }
-        gs[g] = acc;
+        rating[g] = b0 + ((group_top > 1 && per > 1) ? b1 : 0.f);
     }
-    // the best `keep` groups stay; the others are marked by a negative group score
-    for (int drop = 0; drop < groups - keep; ++drop) {
-        int worst = -1;
-        for (int g = 0; g < groups; ++g)
-            if (gs[g] >= 0.f && (worst < 0 || gs[g] <= gs[worst])) worst = g;      // (<=: among equals the higher index goes)
-        gs[worst] = -1.f;
+    __syncwarp();
+    for (int g = lane; g < groups; g += 32) {                        // kept: fewer than `keep` groups rate higher (equal ratings: the lower index first)
+        int ahead = 0;
+        for (int h = 0; h < groups; ++h) ahead += (rating[h] > rating[g]) || (rating[h] == rating[g] && h < g);
+        kept[g] = ahead < keep ? 1.f : 0.f;
     }
+    __syncwarp();
     float total = 0.f;
     for (int k = 0; k < top; ++k) {
-        int best = -1;
-        for (int e = 0; e < E; ++e) {
-            if (gs[e / per] < 0.f || s[e] < 0.f) continue;
-            if (best < 0 || s[e] > s[best]) best = e;
+        float bv = -1.f;
+        int be = -1;
+        for (int e = lane; e < E; e += 32)
+            if (kept[e / per] != 0.f && s[e] > bv) { bv = s[e]; be = e; }      // (taken scores are -1; ascending e: the lower index wins a tie)
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const int oe = __shfl_xor_sync(0xffffffffu, be, o);
+            if (oe >= 0 && (ov > bv || (ov == bv && (be < 0 || oe < be)))) { bv = ov; be = oe; }
         }
-        idx[(size_t)t * top + k] = best;
-        wts[(size_t)t * top + k] = s[best];
-        total += s[best];
-        s[best] = -1.f;                                              // taken
+        total += bv;
+        if (lane == 0) { idx[(size_t)t * top + k] = be; wts[(size_t)t * top + k] = bv; }
+        if ((be & 31) == lane) s[be] = -1.f;
+        __syncwarp();
     }
-    for (int k = 0; k < top; ++k) wts[(size_t)t * top + k] *= renorm ? scale / total : scale;
+    for (int k = lane; k < top; k += 32) wts[(size_t)t * top + k] *= renorm ? scale / total : scale;
 }
 
 // one CTA.  pairs P = T * top.  tiles: int32 [max_tiles][4] = (expert, first row, rows, 0); meta[0] = number of tiles.
@@ -348,10 +353,8 @@ extern "C" int ttie_moe_route(const float* logits, int T, int E, int groups, int
     if (E < 1 || E > MAX_EXPERTS || groups < 1 || E % groups || keep < 1 || keep > groups || top < 1 || top > keep * (E / groups)
         || group_top < 1 || group_top > 2)
         TTIE_FAIL("moe_route: %d experts in %d groups, keep %d, group score of %d, top %d", E, groups, keep, group_top, top);
-    int threads = 64;
-    while (threads > 1 && (size_t)threads * (E + groups) * sizeof(float) > 40 * 1024) threads >>= 1;
-    TTIE_LAUNCH(moe_route_kernel, ceil_div(T, threads), threads, (size_t)threads * (E + groups) * sizeof(float), (cudaStream_t)stream,
-                logits, T, E, groups, keep, group_top, top, scale, renorm, idx, wts);
+    TTIE_LAUNCH(moe_route_kernel, ceil_div(T, ROUTE_WARPS), ROUTE_WARPS * 32, (size_t)ROUTE_WARPS * (E + 2 * groups) * sizeof(float),
+                (cudaStream_t)stream, logits, T, E, groups, keep, group_top, top, scale, renorm, idx, wts);
     TTIE_CHECK_LAUNCH("moe_route");
     return 0;
 }
