@@ -291,10 +291,10 @@ class OpRecorder:
     afterwards, and its algorithmic bytes and flops from the shapes."""
     NAMES = ("embed", "add_rmsnorm", "rmsnorm_rows", "linear", "linear_swiglu", "rope_table", "rope_store", "paged_attention",
              "scale_add_layernorm", "cast_rows", "latent_store", "latent_query", "gate_heads", "batched_linear", "causal_conv",
-             "rglru_scan", "glu", "moe_route", "moe_plan", "grouped_linear", "moe_combine")
+             "rglru_scan", "glu", "linear_glu", "grouped_glu", "moe_route", "moe_plan", "grouped_linear", "moe_combine")
 
     def __init__(self, ops):
-        self.ops, self.calls, self.orig = ops, [], {}
+        self.ops, self.calls, self.orig, self.depth = ops, [], {}, 0
 
     def __enter__(self):
         for n in self.NAMES:
@@ -309,8 +309,13 @@ class OpRecorder:
 
     def _wrap(self, name, fn):
         def call(*args, **kw):
-            out = fn(*args, **kw)
-            self.calls.append((name, fn, args, kw, out))
+            self.depth += 1                                      # (an operation made of others is noted whole, not its parts)
+            try:
+                out = fn(*args, **kw)
+            finally:
+                self.depth -= 1
+            if self.depth == 0:
+                self.calls.append((name, fn, args, kw, out))
             return out
         return call
 
@@ -330,14 +335,14 @@ def op_cost(name, args, kw, out, kv_lens, window):
     """(bytes that must move, flops) of one recorded call, from its shapes."""
     import torch
     flops = 0
-    if name in ("linear", "linear_swiglu"):
+    if name in ("linear", "linear_swiglu", "linear_glu"):
         x, w = args[0], args[1]
         flops = 2 * x.shape[0] * w.shape[0] * w.shape[1]
         return _tensor_bytes([x, w, out]), flops
     if name == "batched_linear":
         x, w = args[0], args[1]
         return _tensor_bytes([w, out]) + x.numel() * x.element_size(), 2 * x.shape[0] * x.shape[1] * w.shape[1] * w.shape[2]
-    if name == "grouped_linear":
+    if name in ("grouped_linear", "grouped_glu"):
         x, w, plan = args[0], args[1], args[2]
         rows = plan["pairs"]
         return _tensor_bytes([w, out]) + rows * w.shape[2] * x.element_size(), 2 * rows * w.shape[1] * w.shape[2]
@@ -377,7 +382,7 @@ def time_ops(eng, entries_fn, pk, kv_lens, window, iters=8):
         b, f = op_cost(name, args, kw, out, kv_lens, window)
         ideal = max(b / (pk["hbm_gbs"] * 1e9), f / (pk["bf16_tflops"] * 1e12)) * 1e6
         key = name
-        if name in ("linear", "batched_linear", "grouped_linear", "linear_swiglu"):
+        if name in ("linear", "batched_linear", "grouped_linear", "linear_swiglu", "linear_glu", "grouped_glu"):
             w = args[1]
             key = f"{name} {list(w.shape)}"
         r = rows.setdefault(key, {"calls": 0, "us": 0.0, "ideal_us": 0.0})

@@ -27,6 +27,9 @@ struct SkinnyParams {
     int M, N, K;
     int kslice;            // K range of one CTA (multiple of 128)
     int up_offset;         // SwiGLU: row offset of the up projection inside w (and bias)
+    // the gated unit's constants: min(g, limit) * sigmoid(alpha * min(g, limit)) * (clamp(u, -limit, limit) + shift); limit <= 0: no
+    // clamps.  alpha 1, no limit, shift 0 is SwiGLU.
+    float glu_alpha = 1.f, glu_limit = 0.f, glu_shift = 0.f;
 };
 
 __device__ __forceinline__ uint4 ld_stream(const void* p) {
@@ -150,9 +153,11 @@ skinny_gemm_kernel(const SkinnyParams p) {
         if (EPI == 2) {
             const int row = n0 + r + 8 * (c >> 1);
             if (row >= p.N) continue;
-            const float g = v[0] + (p.bias ? __bfloat162float(p.bias[row]) : 0.f);
-            const float u = v[NSET - 1] + (p.bias ? __bfloat162float(p.bias[row + p.up_offset]) : 0.f);
-            reinterpret_cast<__nv_bfloat16*>(p.out)[(long long)m * p.ldo + row] = __float2bfloat16_rn(g / (1.f + expf(-g)) * u);
+            float g = v[0] + (p.bias ? __bfloat162float(p.bias[row]) : 0.f);
+            float u = v[NSET - 1] + (p.bias ? __bfloat162float(p.bias[row + p.up_offset]) : 0.f);
+            if (p.glu_limit > 0.f) { g = fminf(g, p.glu_limit); u = fminf(fmaxf(u, -p.glu_limit), p.glu_limit); }
+            reinterpret_cast<__nv_bfloat16*>(p.out)[(long long)m * p.ldo + row] =
+                __float2bfloat16_rn(g / (1.f + expf(-p.glu_alpha * g)) * (u + p.glu_shift));
             continue;
         }
 #pragma unroll
@@ -213,6 +218,15 @@ extern "C" int ttie_skinny_gemm(const void* x, long long ldx, const void* w, lon
                                 long long ldo, int M, int N, int K, int kslice, int epilogue, int up_offset, void* stream) {
     return ttie_skinny_gemm_tuned(x, ldx, w, ldw, bias, out, ldo, M, N, K, kslice, epilogue, up_offset, 0, stream);
 }
+static thread_local float g_glu[3] = {1.f, 0.f, 0.f};
+// the gated-unit epilogue (2) with constants other than SwiGLU's: alpha, limit (<= 0: none), shift
+extern "C" int ttie_skinny_gemm_glu(const void* x, long long ldx, const void* w, long long ldw, void* out, long long ldo, int M, int F,
+                                    int K, float alpha, float limit, float shift, void* stream) {
+    g_glu[0] = alpha; g_glu[1] = limit; g_glu[2] = shift;
+    const int rc = ttie_skinny_gemm_tuned(x, ldx, w, ldw, nullptr, out, ldo, M, F, K, (K + 127) / 128 * 128, 2, F, 0, stream);
+    g_glu[0] = 1.f; g_glu[1] = 0.f; g_glu[2] = 0.f;
+    return rc;
+}
 // unroll: 0 = chosen from kslice; 2 or 4 = 32-key blocks per register buffer (rows <= 8 only); + 16 = two sets of 16
 // weight rows per CTA (plain epilogues; halves the 32-key blocks per buffer).
 extern "C" int ttie_skinny_gemm_tuned(const void* x, long long ldx, const void* w, long long ldw, const void* bias, void* out,
@@ -231,6 +245,7 @@ extern "C" int ttie_skinny_gemm_tuned(const void* x, long long ldx, const void* 
     p.x = (const __nv_bfloat16*)x; p.ldx = ldx; p.w = (const __nv_bfloat16*)w; p.ldw = ldw;
     p.bias = (const __nv_bfloat16*)bias; p.out = out; p.ldo = ldo; p.M = M; p.N = N; p.K = K;
     p.kslice = kslice; p.up_offset = up_offset;
+    p.glu_alpha = g_glu[0]; p.glu_limit = g_glu[1]; p.glu_shift = g_glu[2];
     cudaStream_t s = (cudaStream_t)stream;
     switch (epilogue) {
         case 0: return dispatch<0>(p, splits, unroll, s);

@@ -213,22 +213,29 @@ template <> struct VecOf<__nv_bfloat16> { static constexpr int N = 8; using V = 
 #pragma unroll
         for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(h[i]); o[2 * i] = f.x; o[2 * i + 1] = f.y; } } };
 
+// glu_F > 0: the matrix holds F gate rows, then F up rows; a warp then owns two gate rows and the two up rows that go with them
+// and writes the gated unit's output [rows, F] (constants as in glu_kernel) - the [rows, 2F] product never leaves the SM.
+struct GluConst { int F; float alpha, limit, shift; };
 template <typename T, typename TO, int MT>
 __global__ void __launch_bounds__(GV_WARPS * 32)
 grouped_gemv_kernel(const T* __restrict__ A, long long lda, const int* __restrict__ row_of, int row_div, const T* __restrict__ W,
                     long long w_stride, long long ldw, TO* __restrict__ C, long long ldc, const int* __restrict__ tiles,
-                    const int* __restrict__ meta, int N, int K) {
+                    const int* __restrict__ meta, int N, int K, GluConst glu) {
     constexpr int VN = VecOf<T>::N;
     TTIE_PDL_ENTRY();
     const int tile = blockIdx.y;
     if (tile >= meta[0]) return;
     const int expert = tiles[4 * tile], r0 = tiles[4 * tile + 1], rows = tiles[4 * tile + 2];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n0 = (blockIdx.x * GV_WARPS + warp) * GV_ROWS;
-    if (n0 >= N) return;
+    const bool gated = glu.F > 0;
+    const int n0 = (blockIdx.x * GV_WARPS + warp) * (gated ? GV_ROWS / 2 : GV_ROWS);
+    if (n0 >= (gated ? glu.F : N)) return;
     const T* wrow[GV_ROWS];
 #pragma unroll
-    for (int r = 0; r < GV_ROWS; ++r) wrow[r] = W + (size_t)expert * w_stride + (size_t)min(n0 + r, N - 1) * ldw;
+    for (int r = 0; r < GV_ROWS; ++r) {
+        const int n = gated ? (r < 2 ? min(n0 + r, glu.F - 1) : glu.F + min(n0 + r - 2, glu.F - 1)) : min(n0 + r, N - 1);
+        wrow[r] = W + (size_t)expert * w_stride + (size_t)n * ldw;
+    }
     for (int m0 = 0; m0 < rows; m0 += MT) {
         const T* arow[MT];
 #pragma unroll
@@ -258,7 +265,17 @@ grouped_gemv_kernel(const T* __restrict__ A, long long lda, const int* __restric
         for (int m = 0; m < MT; ++m)
 #pragma unroll
             for (int r = 0; r < GV_ROWS; ++r) acc[m][r] = warp_sum(acc[m][r]);
-        if (lane == 0) {
+        if (lane == 0 && gated) {
+#pragma unroll
+            for (int m = 0; m < MT; ++m)
+#pragma unroll
+                for (int r = 0; r < GV_ROWS / 2; ++r) {
+                    if (m0 + m >= rows || n0 + r >= glu.F) continue;
+                    float g = acc[m][r], u = acc[m][r + 2];
+                    if (glu.limit > 0.f) { g = fminf(g, glu.limit); u = fminf(fmaxf(u, -glu.limit), glu.limit); }
+                    C[(size_t)(r0 + m0 + m) * ldc + n0 + r] = from_f32<TO>(g / (1.0f + expf(-glu.alpha * g)) * (u + glu.shift));
+                }
+        } else if (lane == 0) {
 #pragma unroll
             for (int m = 0; m < MT; ++m)
 #pragma unroll
@@ -370,15 +387,18 @@ extern "C" int ttie_moe_plan(const int* idx, int P, int E, int max_tiles, int* o
 
 extern "C" int ttie_grouped_gemm(const void* A, long long lda, const int* row_of, int row_div, const void* W, long long w_stride,
                                  long long ldw, void* C, long long ldc, const int* tiles, const int* meta, int max_tiles, int N, int K,
-                                 int dtype, int out_dtype, int few_rows, void* stream) {
+                                 int dtype, int out_dtype, int few_rows, int glu_F, float glu_alpha, float glu_limit, float glu_shift,
+                                 void* stream) {
     if (max_tiles <= 0 || N <= 0) return 0;
     if (max_tiles > 65535) TTIE_FAIL("grouped_gemm: %d row tiles in one launch", max_tiles);
     cudaStream_t s = (cudaStream_t)stream;
     const int vn = dtype == kF32 ? 4 : 8, esz = dtype == kF32 ? 4 : 2;
     if (few_rows && K % vn == 0 && lda % vn == 0 && ldw % vn == 0 && w_stride % vn == 0 && (((uintptr_t)A | (uintptr_t)W) & 15) == 0 && esz) {
-        const dim3 g(ceil_div(N, GV_WARPS * GV_ROWS), max_tiles);
+        if (glu_F > 0 && N != 2 * glu_F) TTIE_FAIL("grouped_gemm: a gated epilogue of width %d on a matrix of %d rows", glu_F, N);
+        const GluConst glu{glu_F, glu_alpha, glu_limit, glu_shift};
+        const dim3 g(glu_F > 0 ? ceil_div(glu_F, GV_WARPS * GV_ROWS / 2) : ceil_div(N, GV_WARPS * GV_ROWS), max_tiles);
 #define GV(TT, TO) TTIE_LAUNCH((grouped_gemv_kernel<TT, TO, 4>), g, GV_WARPS * 32, 0, s, (const TT*)A, lda, row_of, row_div > 0 ? row_div : 1, (const TT*)W, \
-                               w_stride, ldw, (TO*)C, ldc, tiles, meta, N, K)
+                               w_stride, ldw, (TO*)C, ldc, tiles, meta, N, K, glu)
         if (dtype == kF32 && out_dtype == kF32) GV(float, float);
         else if (dtype == kBF16 && out_dtype == kBF16) GV(__nv_bfloat16, __nv_bfloat16);
         else if (dtype == kBF16 && out_dtype == kF32) GV(__nv_bfloat16, float);
@@ -387,6 +407,7 @@ extern "C" int ttie_grouped_gemm(const void* A, long long lda, const int* row_of
         TTIE_CHECK_LAUNCH("grouped_gemm (few rows)");
         return 0;
     }
+    if (glu_F > 0) TTIE_FAIL("grouped_gemm: the gated epilogue exists in the few-rows form only");
     const dim3 grid(ceil_div(N, BN), max_tiles);
 #define GG(TT, TO) TTIE_LAUNCH((grouped_gemm_kernel<TT, TO>), grid, 256, 0, s, (const TT*)A, lda, row_of, row_div > 0 ? row_div : 1, (const TT*)W, \
                                w_stride, ldw, (TO*)C, ldc, tiles, meta, N, K)

@@ -72,7 +72,8 @@ _SIGNATURES = {
     "ttie_moe_route": [_c_void, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_void, _c_void, _c_void],
     "ttie_moe_plan": [_c_void, _c_int, _c_int, _c_int, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void],
     "ttie_grouped_gemm": [_c_void, _c_ll, _c_void, _c_int, _c_void, _c_ll, _c_ll, _c_void, _c_ll, _c_void, _c_void, _c_int, _c_int, _c_int,
-                          _c_int, _c_int, _c_int, _c_void],
+                          _c_int, _c_int, _c_int, _c_int, _c_float, _c_float, _c_float, _c_void],
+    "ttie_skinny_gemm_glu": [_c_void, _c_ll, _c_void, _c_ll, _c_void, _c_ll, _c_int, _c_int, _c_int, _c_float, _c_float, _c_float, _c_void],
     "ttie_gather_rows": [_c_void, _c_ll, _c_void, _c_int, _c_int, _c_int, _c_void, _c_int, _c_void],
     "ttie_moe_combine": [_c_void, _c_int, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_void, _c_int, _c_void],
     "ttie_sample": [_c_void, _c_int, _c_int, _c_void, _c_void, _c_void, _c_void, _c_void],
@@ -981,6 +982,37 @@ class CudaOps:
             self._grouped_mm = False                                    # this build has none for the device: the own kernel serves
             return None
 
+    def linear_glu(self, x, w_gu, hidden, alpha=1.0, limit=0.0, shift=0.0):
+        """The gated unit's activation of x @ [Wg; Wu].T -> [M, hidden].  With SwiGLU's constants this is ``linear_swiglu`` and
+        its fused forms; with others, up to 8 rows run the weight-streaming product with the unit in its epilogue (where that
+        form measured faster for the shape), more rows the product and the activation kernel."""
+        if alpha == 1.0 and not limit and shift == 0.0:
+            return self.linear_swiglu(x, w_gu, None, hidden)
+        if x.dtype == torch.bfloat16 and self._skinny_ok(x, w_gu) and self._fused_few_rows_wins(x, w_gu, None, hidden):
+            M, K = x.shape
+            act = torch.empty((M, hidden), dtype=x.dtype, device=x.device)
+            self._check(self.lib.ttie_skinny_gemm_glu(_ptr(x), x.stride(0), _ptr(w_gu), w_gu.stride(0), _ptr(act), hidden, M, hidden, K,
+                                                      float(alpha), float(limit or 0.0), float(shift), self._stream(x)), "skinny_gemm_glu")
+            self.launches += 1
+            return act
+        return self.glu(self.linear(x, w_gu, None), hidden, alpha, limit, shift)
+
+    def grouped_glu(self, x, w_gu, plan, gather_div, hidden, alpha=1.0, limit=0.0, shift=0.0):
+        """The experts' gate/up products over rows sorted by expert, then the gated unit: [pairs, hidden].  Few rows: one
+        kernel (the unit in the weight-streaming product's epilogue); many: the grouped product and the activation kernel."""
+        few = plan["pairs"] <= self.grouped_few_rows
+        E, N, K = w_gu.shape
+        vn = 4 if x.dtype == torch.float32 else 8
+        if few and K % vn == 0 and x.stride(0) % vn == 0:
+            out = torch.empty((plan["pairs"], hidden), dtype=x.dtype, device=x.device)
+            self._check(self.lib.ttie_grouped_gemm(_ptr(x), x.stride(0), _ptr(plan["pair_of_pos"]) if gather_div else None, int(gather_div),
+                                                   _ptr(w_gu), w_gu.stride(0), w_gu.stride(1), _ptr(out), hidden, _ptr(plan["tiles"]),
+                                                   _ptr(plan["meta"]), plan["max_tiles"], N, K, self._dt(x), self._dt(out), 1, int(hidden),
+                                                   float(alpha), float(limit or 0.0), float(shift), self._stream(x)), "grouped_gemm (gated)")
+            self.launches += 1
+            return out
+        return self.glu(self.grouped_linear(x, w_gu, plan, gather_div), hidden, alpha, limit, shift)
+
     def grouped_linear(self, x, w, plan, gather_div=0, out_dtype=None):
         """Rows sorted by expert times their expert's matrix: w [E, N, K]; row ``pos`` of the result is
         x[pair_of_pos[pos] // gather_div] @ w[e].T (``gather_div`` 0: x[pos]).  Few rows: a kernel that streams each tile's
@@ -995,8 +1027,8 @@ class CudaOps:
         out = torch.empty((plan["pairs"], N), dtype=out_dtype or x.dtype, device=x.device)
         self._check(self.lib.ttie_grouped_gemm(_ptr(x), x.stride(0), _ptr(plan["pair_of_pos"]) if gather_div else None, int(gather_div),
                                                _ptr(w), w.stride(0), w.stride(1), _ptr(out), N, _ptr(plan["tiles"]), _ptr(plan["meta"]),
-                                               plan["max_tiles"], N, K, self._dt(x), self._dt(out), 1 if few else 0, self._stream(x)),
-                    "grouped_gemm")
+                                               plan["max_tiles"], N, K, self._dt(x), self._dt(out), 1 if few else 0, 0, 1.0, 0.0, 0.0,
+                                               self._stream(x)), "grouped_gemm")
         self.launches += 1
         return out
 

@@ -80,5 +80,5 @@ class GLU(FeedForward):
         return [self.w_gu, self.w_down]
 
     def forward(self, x: torch.Tensor, ctx: StepContext, partial_ok: bool = True) -> torch.Tensor:
-        act = self.ops.glu(self.ops.linear(x, self.w_gu, None), self.hidden, self.alpha, self.limit or 0.0, self.shift)
+        act = self.ops.linear_glu(x, self.w_gu, self.hidden, self.alpha, self.limit or 0.0, self.shift)
         return self.ops.linear(act, self.w_down, None, partial_ok=partial_ok)

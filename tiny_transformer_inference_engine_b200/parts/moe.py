@@ -75,8 +75,7 @@ class GroupedMoE(FeedForward):
         logits = ops.linear(x, self.w_router, None, out_dtype=torch.float32)
         idx, wts = ops.moe_route(logits, self.groups, self.keep, self.group_top, self.top, self.scale, self.renorm)
         plan = ops.moe_plan(idx, self.experts)
-        h = ops.grouped_linear(x, self.w_gu, plan, gather_div=self.top)                  # [P, 2F], rows sorted by expert
-        act = ops.glu(h, self.hidden, self.alpha, self.limit or 0.0, self.shift)
+        act = ops.grouped_glu(x, self.w_gu, plan, self.top, self.hidden, self.alpha, self.limit or 0.0, self.shift)   # [P, F], rows sorted by expert
         y = ops.grouped_linear(act, self.w_down, plan, out_dtype=torch.float32)          # [P, d] float32
         shared = self.shared.forward(x, ctx, partial_ok=False) if self.shared is not None else None
         return ops.moe_combine(y, plan, wts, shared, T, self.d_model)                    # float32 [T, d]
