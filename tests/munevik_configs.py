@@ -71,3 +71,9 @@ MUN_G = {"architecture": "Munevik", "vocab": 80, "width": 32, "postln_alpha": 1.
     recurrent_layer(32, 2, 3, dense_mlp(48, 2.0)), recurrent_layer(64, 64, 2, None)]}
 MUN_H = {"architecture": "Munevik", "vocab": 80, "width": 32, "postln_alpha": 1.0, "norm": {"eps": 1e-6}, "layers": [
     attention_layer(2, 8, 8, 8, 24, 16, None), attention_layer(4, 4, 4, 12, 12, 3, dense_mlp(48, 2.0))]}
+
+# a cache row wider than any tensor-core attention kernel takes (300 + 12 values, padded to 320): the general kernel
+MUN_I = {"architecture": "Munevik", "vocab": 90, "width": 64, "postln_alpha": 1.0, "norm": {"eps": 1e-6}, "layers": [
+    attention_layer(3, 20, 12, 24, 300, 50, dense_mlp(48, 1.0)),
+    attention_layer(2, 16, 12, 16, 300, 9, None, kv_from=0),
+]}

@@ -312,8 +312,8 @@ def test_refuses_sizes_it_cannot_take(ops):
     from tiny_transformer_inference_engine_b200.ops import KernelError
     with pytest.raises(KernelError, match="head size 18"):
         attention_case(ops, "float32", 2, 1, 18, 4, [(5, 5)])
-    with pytest.raises(KernelError, match="head size 272"):
-        attention_case(ops, "bfloat16", 2, 1, 272, 4, [(5, 5)])
+    with pytest.raises(KernelError, match="head size 528"):
+        attention_case(ops, "bfloat16", 2, 1, 528, 4, [(5, 5)])
     with pytest.raises(KernelError, match="not supported"):
         ops.linear(torch.zeros(2, 2, dtype=torch.float16, device=DEV), torch.zeros(2, 2, dtype=torch.float16, device=DEV), None) \
             if False else ops.embed(torch.zeros(1, dtype=torch.int32, device=DEV),

@@ -13,12 +13,12 @@ from tiny_transformer_inference_engine_b200.parts.base import PartSpec, StepCont
 from tiny_transformer_inference_engine_b200.registry import build_part
 from tiny_transformer_inference_engine_b200.weights import random_tensors
 
-from munevik_configs import MUN_A, MUN_B, MUN_C, MUN_D, MUN_E, MUN_F, MUN_G, MUN_H
+from munevik_configs import MUN_A, MUN_B, MUN_C, MUN_D, MUN_E, MUN_F, MUN_G, MUN_H, MUN_I
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
-CONFIGS = {"A": MUN_A, "B": MUN_B, "C": MUN_C, "D": MUN_D, "E": MUN_E, "F": MUN_F, "G": MUN_G, "H": MUN_H}
+CONFIGS = {"A": MUN_A, "B": MUN_B, "C": MUN_C, "D": MUN_D, "E": MUN_E, "F": MUN_F, "G": MUN_G, "H": MUN_H, "I": MUN_I}
 
 
 @pytest.fixture(scope="module")
@@ -75,13 +75,13 @@ def check(got, exp, dtype):
 
 # ------------------------------------------------------------------------------------------ the whole model, four cuts
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E", "F", "G", "H"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E", "F", "G", "H", "I"])
 def test_schedules_against_plain_model(name, dtype):
     cfg = CONFIGS[name]
     w = weights_for(cfg, 5 + ord(name))
     reqs = requests(cfg, [1, 2, 37, 70, 101, 23], seed=3)
     exp = expected_for(cfg, w, reqs, dtype)
-    page = {"A": 16, "B": 8, "C": 4, "D": 32, "E": 16, "F": 8, "G": 16, "H": 2}[name]
+    page = {"A": 16, "B": 8, "C": 4, "D": 32, "E": 16, "F": 8, "G": 16, "H": 2, "I": 16}[name]
     for cut in (tu.whole, tu.prefill_then_decode, tu.portions, tu.mixed):
         steps = cut(reqs)
         tokens = tu.max_live_tokens(steps, rounding=page)

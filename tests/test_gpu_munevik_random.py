@@ -44,7 +44,7 @@ def draw_config(seed):
                                               kv_from=j, scale=rng.choice([None, 0.3])))
             else:
                 rot = 2 * rng.randint(1, 8)
-                layers.append(attention_layer(heads, dim, rot, vdim, rng.randint(6, 240 - rot), window, mlp(),
+                layers.append(attention_layer(heads, dim, rot, vdim, rng.choice([rng.randint(6, 240 - rot), rng.randint(6, 500 - rot)]), window, mlp(),
                                               base=rng.choice([50.0, 10000.0, 500000.0])))
                 owners.append(i)
         else:

@@ -268,12 +268,12 @@ def test_sizes_the_kernels_do_not_take_are_refused_at_construction():
     from tiny_transformer_inference_engine_b200.ops import KernelError
     import tiny_transformer_inference_engine_b200.weights as weights
     small = dict(TINY_A, d_model=40, num_heads=4)                      # head size 10
-    wide = dict(TINY_A, d_model=640, num_heads=2)                      # head size 320
+    wide = dict(TINY_A, d_model=1056, num_heads=2)                     # head size 528
     calls = []
     inner = weights.loader.place
     weights.loader.place = lambda *a, **k: calls.append(1) or inner(*a, **k)
     try:
-        for cfg, what in ((small, "head size 10"), (wide, "head size 320")):
+        for cfg, what in ((small, "head size 10"), (wide, "head size 528")):
             with pytest.raises(KernelError, match=what):
                 Engine(ModelConfig.from_dict(cfg), {}, EngineConfig(dtype="float32", device=DEV))
     finally:

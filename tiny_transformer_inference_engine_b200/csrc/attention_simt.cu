@@ -1,5 +1,5 @@
 // Paged causal attention, general form: any mix of prompt portions and single decoded tokens,
-// any number of heads and kv heads, head sizes that are multiples of 4 up to 256, any page
+// any number of heads and kv heads, head sizes that are multiples of 4 up to 512, any page
 // size, optional window, float32 or bfloat16 storage with float32 arithmetic throughout
 // (scores, running maximum and sum, output accumulators; expf, not a fast approximation).
 // It is the attention of the float32 path and the fallback of the bfloat16 path.
@@ -388,8 +388,13 @@ int dispatch(const AttnParams& p, int T_tokens, cudaStream_t s) {
         case 6: return launch<T, 6>(p, T_tokens, s);
         case 7: return launch<T, 7>(p, T_tokens, s);
         case 8: return launch<T, 8>(p, T_tokens, s);
+        // wider rows (latent attention: a cache row is the whole latent): the same kernel with more columns per lane
+        case 9: case 10: return launch<T, 10>(p, T_tokens, s);
+        case 11: case 12: return launch<T, 12>(p, T_tokens, s);
+        case 13: case 14: return launch<T, 14>(p, T_tokens, s);
+        case 15: case 16: return launch<T, 16>(p, T_tokens, s);
     }
-    TTIE_FAIL("paged_attention: head size %d not supported (multiples of 4 up to 256)", p.D);
+    TTIE_FAIL("paged_attention: head size %d not supported (multiples of 4 up to 512)", p.D);
 }
 }  // namespace
 
@@ -404,7 +409,7 @@ extern "C" int ttie_paged_attention(const void* q, long long q_stride, const voi
                                     int max_q_len, float scale, int window, int num_splits, int split_len,
                                     float* scratch, int dtype, void* stream) {
     if (T <= 0 || num_seqs <= 0) return 0;
-    if (D % 4 || D > 256 || D <= 0) TTIE_FAIL("paged_attention: head size %d not supported (multiples of 4 up to 256)", D);
+    if (D % 4 || D > 512 || D <= 0) TTIE_FAIL("paged_attention: head size %d not supported (multiples of 4 up to 512)", D);
     if (Hkv <= 0 || Hq % Hkv) TTIE_FAIL("paged_attention: %d heads are not a multiple of %d kv heads", Hq, Hkv);
     if (page_size <= 0) TTIE_FAIL("paged_attention: page size %d", page_size);
     if (num_splits < 1) num_splits = 1;

@@ -191,10 +191,10 @@ class CudaOps:
 
     def check_attention(self, dtype, num_heads, num_kv_heads, head_dim, page_size):
         """Raises unless some attention kernel here takes the sizes: the general kernel takes every head size that is
-        a multiple of 4 up to 256, any head counts and any page size (the tensor-core kernels cover subsets of that)."""
+        a multiple of 4 up to 512, any head counts and any page size (the tensor-core kernels cover subsets of that)."""
         self.check_dtype(dtype)
-        if head_dim <= 0 or head_dim % 4 or head_dim > 256:
-            raise KernelError(f"attention: head size {head_dim} not supported (multiples of 4 up to 256)")
+        if head_dim <= 0 or head_dim % 4 or head_dim > 512:
+            raise KernelError(f"attention: head size {head_dim} not supported (multiples of 4 up to 512)")
         if num_kv_heads <= 0 or num_heads % num_kv_heads:
             raise KernelError(f"attention: {num_heads} heads are not a multiple of {num_kv_heads} kv heads")
         if page_size < 1:
