@@ -53,7 +53,7 @@ class MunevikConfig:
             raise ConfigError("'layers' must list at least one layer")
         for i, L in enumerate(self.layers):
             where = f"layers[{i}]"
-            _need(L, ("type", "mixer", "mlp"), where)
+            _need(L, ("type", "mixer"), where)                       # ("mlp" absent reads like null: no feed-forward)
             m = L["mixer"]
             if L["type"] == "latent_attention":
                 _need(m, ("heads", "dim", "rot_dim", "vdim", "kv_rank", "scale", "mask", "rot"), f"{where}.mixer")
@@ -86,7 +86,7 @@ class MunevikConfig:
                     raise ConfigError(f"{where}.mixer: width {m['width']} is not a multiple of {m['blocks']} blocks")
             else:
                 raise ConfigError(f"{where}.type {L['type']!r} unknown; known: {MIXERS}")
-            f = L["mlp"]
+            f = L.get("mlp")
             if f is None:
                 continue
             _need(f, ("kind",), f"{where}.mlp")

@@ -50,7 +50,7 @@ def munevik(config: MunevikConfig) -> ModelSpec:
         else:
             mixer = PartSpec("rglru", f"{p}.mix", {"d_model": d, "width": m["width"], "blocks": m["blocks"], "taps": m["conv"],
                                                    "decay": RGLRU_DECAY})
-        f = L["mlp"]
+        f = L.get("mlp")
         if f is None:
             ffn = None
         elif f["kind"] == "dense":
