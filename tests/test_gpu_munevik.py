@@ -128,6 +128,40 @@ def test_greedy_generation_through_the_scheduler(graphs):
     assert got == want
 
 
+def test_command_line_and_trace_runner_with_a_model_folder(tmp_path):
+    """A folder written in the random-weights mode (bfloat16 on disk), generated from by the command line and replayed by the
+    trace runner: the architecture is picked from config.json by both."""
+    import json, os, subprocess, sys
+    import numpy as np
+    from safetensors.torch import load_file
+    from tiny_transformer_inference_engine_b200 import write_random_model
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cfg = dict(MUN_B, max_seq_len=96)
+    folder = write_random_model(ModelConfig.from_dict(cfg), 13, str(tmp_path / "model"), std=0.08, perturb_norms=True, store_dtype="bfloat16")
+    w = load_file(os.path.join(folder, "model.safetensors"))
+    prompt = [4, 100, 7, 7, 23]
+    run = subprocess.run([sys.executable, "-m", "tiny_transformer_inference_engine_b200", "--model", folder, "--tokens", "6", "--greedy",
+                          "--dtype", "float32", "--num-gpu-blocks", "16", "--prompt-ids", ",".join(map(str, prompt))],
+                         cwd=root, capture_output=True, text=True, timeout=600)
+    assert run.returncode == 0, run.stderr[-2000:]
+    toks = list(prompt)
+    for _ in range(6):
+        toks.append(int(torch.argmax(pm.forward(cfg, w, toks)[-1])))
+    assert json.loads(run.stdout.strip().split("\n")[-1])["generated_ids"] == toks[len(prompt):]
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": toks[:7], "want": [0, 6]}], "end": []},
+             {"step": 1, "entries": [{"id": "a", "tokens": toks[7:9], "want": [1]}, {"id": "b", "tokens": toks[:3], "want": []}], "end": ["a"]},
+             {"step": 2, "entries": [{"id": "b", "tokens": toks[3:4], "want": [0]}], "end": ["b"]}]
+    out = tmp_path / "out"
+    run = subprocess.run([os.path.join(root, "bin", "trace_run"), "--model", folder, "--dtype", "float32", "--out", str(out), "--max-tokens", "128"],
+                         input="\n".join(json.dumps(s) for s in steps) + "\n", cwd=root, capture_output=True, text=True, timeout=600)
+    assert run.returncode == 0, run.stderr[-2000:]
+    assert [l for l in run.stdout.split("\n") if l.startswith("done")] == ["done 0", "done 1", "done 2"]
+    exp = pm.forward(cfg, w, toks)
+    for name, rows in (("0.f32", [0, 6]), ("1.f32", [8]), ("2.f32", [3])):
+        got = torch.from_numpy(np.fromfile(str(out / name), dtype="<f4").reshape(len(rows), cfg["vocab"]))
+        assert ((got.double() - exp[rows]).abs().max() / exp[rows].abs().max()).item() < 1e-4, name
+
+
 def test_repeated_portions_replayed_from_graphs():
     """Steps of one layout (a 40-token prompt: more (token, expert) pairs than the few-rows kernel takes, so the grouped
     products are the many-rows forms) are captured the second time and replayed after that; all three must give the plain
