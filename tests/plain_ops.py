@@ -97,7 +97,7 @@ class PlainOps:
             v_pages[page, :, off, :] = v
 
     def paged_attention(self, qkv, num_heads, num_kv_heads, head_dim, k_pages, v_pages, block_table, page_size,
-                        query_start_loc, seq_lens, num_seqs, max_q_len, max_kv_len, scale, window, out):
+                        query_start_loc, seq_lens, num_seqs, max_q_len, max_kv_len, scale, window, out, softcap=0.0):
         D, G = head_dim, num_heads // num_kv_heads
         qsl, sl = query_start_loc.tolist(), seq_lens.tolist()
         for i in range(num_seqs):
@@ -117,6 +117,8 @@ class PlainOps:
                 vis = vis & (kpos > qpos - window)
             for h in range(num_heads):
                 s = (q[:, h] @ k[:, h // G].T) * scale
+                if softcap:
+                    s = softcap * torch.tanh(s / softcap)
                 s = s.masked_fill(~vis.to(s.device), float("-inf"))
                 out[a:b, h * D:(h + 1) * D] = (torch.softmax(s, dim=-1) @ v[:, h // G]).to(out.dtype)
 

@@ -1,6 +1,7 @@
 from .model_config import ModelConfig, ConfigError, DEFAULT_ARCHITECTURE
 from .munevik_config import MunevikConfig
+from .mizupel_config import MizupelConfig
 from .engine_config import CacheConfig, SchedulerConfig, EngineConfig, COMPUTE_DTYPES
 
-__all__ = ["ModelConfig", "MunevikConfig", "ConfigError", "DEFAULT_ARCHITECTURE", "CacheConfig", "SchedulerConfig",
+__all__ = ["ModelConfig", "MunevikConfig", "MizupelConfig", "ConfigError", "DEFAULT_ARCHITECTURE", "CacheConfig", "SchedulerConfig",
            "EngineConfig", "COMPUTE_DTYPES"]

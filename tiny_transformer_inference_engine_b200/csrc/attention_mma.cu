@@ -30,11 +30,20 @@ struct MmaParams {
     __nv_bfloat16* out;
     int num_seqs, Hq, Hkv;
     float scale_log2; int window;
+    float cap_in, cap_out;              // score softcap: raw score s becomes cap_out * tanh(s * cap_in) (cap_in 0: none)
     int row_tiles, num_splits, split_len;
     float* ws_o; float* ws_ml;
 };
 
 __device__ __forceinline__ unsigned smem_addr(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+// tanh from the hardware's exponential and reciprocal: 1 - 2 / (2^(2x log2 e) + 1); absolute error about 2e-7
+__device__ __forceinline__ float tanh_ex2(float x) {
+    float e, r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(x * 2.8853900817779268f));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(e + 1.0f));
+    return fmaf(-2.0f, r, 1.0f);
+}
 
 __device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
     const int n = valid ? 16 : 0;                                   // 0 source bytes: the 16 bytes are zero-filled
@@ -219,6 +228,7 @@ paged_attn_mma_kernel(const MmaParams p) {
                 for (int e = 0; e < 4; ++e) {
                     const int h = e >> 1;
                     float v = s[i][e];                                 // raw scores; the scale (positive) goes into the exponent's fma
+                    if (p.cap_in != 0.f) v = p.cap_out * tanh_ex2(v * p.cap_in);
                     if (!full) {
                         const int key = kt + i * 8 + 2 * (lane & 3) + (e & 1);
                         if (!(rvalid[h] && key <= rpos[h] && key >= rlo[h] && key < k_hi)) v = -INFINITY;
@@ -497,6 +507,7 @@ paged_attn_cluster_kernel(const MmaParams p) {
                 for (int e = 0; e < 4; ++e) {
                     const int h = e >> 1;
                     float v = s[i][e];                                 // raw scores; the scale (positive) goes into the exponent's fma
+                    if (p.cap_in != 0.f) v = p.cap_out * tanh_ex2(v * p.cap_in);
                     if (!full) {
                         const int key = kt + i * 8 + 2 * (lane & 3) + (e & 1);
                         if (!(rvalid[h] && key <= rpos[h] && key >= rlo[h] && key < k_hi)) v = -INFINITY;
@@ -766,22 +777,22 @@ extern "C" int ttie_attn_cluster_active(int D, int max_q_len, int Hq, int Hkv, i
 extern "C" int ttie_paged_attention_mma_form(const void* q, long long q_stride, const void* k_pages, const void* v_pages,
                                              const int* block_table, int table_width, int page_size, const int* qsl,
                                              const int* seq_lens, void* out, int T, int num_seqs, int Hq, int Hkv, int D,
-                                             int max_q_len, float scale, int window, int num_splits, int split_len,
+                                             int max_q_len, float scale, float softcap, int window, int num_splits, int split_len,
                                              float* scratch, int form, void* stream);
 
 extern "C" int ttie_paged_attention_mma(const void* q, long long q_stride, const void* k_pages, const void* v_pages,
                                         const int* block_table, int table_width, int page_size, const int* qsl,
                                         const int* seq_lens, void* out, int T, int num_seqs, int Hq, int Hkv, int D,
-                                        int max_q_len, float scale, int window, int num_splits, int split_len,
+                                        int max_q_len, float scale, float softcap, int window, int num_splits, int split_len,
                                         float* scratch, void* stream) {
     return ttie_paged_attention_mma_form(q, q_stride, k_pages, v_pages, block_table, table_width, page_size, qsl, seq_lens, out,
-                                         T, num_seqs, Hq, Hkv, D, max_q_len, scale, window, num_splits, split_len, scratch, 0, stream);
+                                         T, num_seqs, Hq, Hkv, D, max_q_len, scale, softcap, window, num_splits, split_len, scratch, 0, stream);
 }
 
 extern "C" int ttie_paged_attention_mma_form(const void* q, long long q_stride, const void* k_pages, const void* v_pages,
                                              const int* block_table, int table_width, int page_size, const int* qsl,
                                              const int* seq_lens, void* out, int T, int num_seqs, int Hq, int Hkv, int D,
-                                             int max_q_len, float scale, int window, int num_splits, int split_len,
+                                             int max_q_len, float scale, float softcap, int window, int num_splits, int split_len,
                                              float* scratch, int form, void* stream) {
     if (T <= 0 || num_seqs <= 0) return 0;
     if (!ttie_attn_mma_supported(D)) TTIE_FAIL("paged_attention_mma: head size %d not supported (multiples of 16 up to 128)", D);
@@ -799,6 +810,7 @@ extern "C" int ttie_paged_attention_mma_form(const void* q, long long q_stride, 
     p.qsl = qsl; p.seq_lens = seq_lens; p.out = (__nv_bfloat16*)out;
     p.num_seqs = num_seqs; p.Hq = Hq; p.Hkv = Hkv;
     p.scale_log2 = scale * 1.4426950408889634f; p.window = window;
+    p.cap_in = softcap > 0.f ? scale / softcap : 0.f; p.cap_out = softcap > 0.f ? softcap / scale : 0.f;
     p.num_splits = num_splits; p.split_len = split_len;
     p.ws_o = scratch; p.ws_ml = scratch ? scratch + (size_t)T * Hq * num_splits * D : nullptr;
     const int rows = max_q_len * (Hq / Hkv);

@@ -29,6 +29,7 @@ struct AttnParams {
     void* out;
     int num_seqs, Hq, Hkv, D;
     float scale; int window;
+    float softcap;                 // > 0: scores pass cap * tanh(score / cap) before mask and softmax
     int row_tiles;                 // tiles of ROWS query rows per (request, kv head)
     int num_splits, split_len;
     float* ws_o; float* ws_ml;     // [T*Hq, num_splits, D] and [T*Hq, num_splits, 2]
@@ -144,7 +145,9 @@ paged_attn_simt_kernel(const AttnParams p) {
 #pragma unroll
             for (int r = 0; r < RPW; ++r) {
                 const bool vis = valid[r] && key < k_hi && key <= pos[r] && key >= lo[r];
-                const float sc = vis ? s[r] * p.scale : -INFINITY;
+                float sv = s[r] * p.scale;
+                if (p.softcap > 0.f) sv = p.softcap * tanhf(sv / p.softcap);
+                const float sc = vis ? sv : -INFINITY;
                 const float m_new = fmaxf(m[r], warp_max(sc));
                 const float alpha = (m[r] == -INFINITY) ? 0.f : expf(m[r] - m_new);
                 pr[r] = vis ? expf(sc - m_new) : 0.f;
@@ -406,7 +409,7 @@ extern "C" long long ttie_attn_scratch_floats(int T, int Hq, int D, int num_spli
 extern "C" int ttie_paged_attention(const void* q, long long q_stride, const void* k_pages, const void* v_pages,
                                     const int* block_table, int table_width, int page_size, const int* qsl,
                                     const int* seq_lens, void* out, int T, int num_seqs, int Hq, int Hkv, int D,
-                                    int max_q_len, float scale, int window, int num_splits, int split_len,
+                                    int max_q_len, float scale, float softcap, int window, int num_splits, int split_len,
                                     float* scratch, int dtype, void* stream) {
     if (T <= 0 || num_seqs <= 0) return 0;
     if (D % 4 || D > 512 || D <= 0) TTIE_FAIL("paged_attention: head size %d not supported (multiples of 4 up to 512)", D);
@@ -418,7 +421,7 @@ extern "C" int ttie_paged_attention(const void* q, long long q_stride, const voi
     p.q = q; p.q_stride = q_stride; p.k_pages = k_pages; p.v_pages = v_pages;
     p.block_table = block_table; p.table_width = table_width; p.page_size = page_size;
     p.qsl = qsl; p.seq_lens = seq_lens; p.out = out;
-    p.num_seqs = num_seqs; p.Hq = Hq; p.Hkv = Hkv; p.D = D; p.scale = scale; p.window = window;
+    p.num_seqs = num_seqs; p.Hq = Hq; p.Hkv = Hkv; p.D = D; p.scale = scale; p.window = window; p.softcap = softcap;
     const int G = Hq / Hkv;
     p.row_tiles = ceil_div(max_q_len * G, ROWS);
     p.num_splits = num_splits; p.split_len = split_len;

@@ -111,6 +111,13 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
 __device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t (&r)[32]) { tmem_ld32(taddr, r); }
 __device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t (&r)[16]) { tmem_ld16(taddr, r); }
 
+// tanh from the hardware's exponential and reciprocal: 1 - 2 / (2^(2x log2 e) + 1); absolute error about 2e-7
+__device__ __forceinline__ float tanh_ex2(float x) {
+    float e, r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(x * 2.8853900817779268f));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(e + 1.0f));
+    return fmaf(-2.0f, r, 1.0f);
+}
 __device__ __forceinline__ float ex2(float x) {                // 2^x, one instruction; 2^-inf = 0
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -147,6 +154,7 @@ struct AttnTcParams {
     __nv_bfloat16* out;
     int num_seqs, Hq, Hkv;
     float scale_log2; int window;
+    float cap_in, cap_out;                                       // score softcap: raw score s becomes cap_out * tanh(s * cap_in) (cap_in 0: none)
     int row_tiles;
     int q_rows;                                                  // rows of the query tile that are staged (a multiple of 32 that covers every request's rows)
     int num_splits, split_len;                                   // keys per CTA along grid y (a multiple of 128); 1: no split
@@ -466,6 +474,10 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
                 tmem_ld32(lane_addr + S_COL + sb * BN + part * SC, sv);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                if (p.cap_in != 0.f) {
+#pragma unroll
+                    for (int i = 0; i < SC; ++i) sv[i] = __float_as_uint(p.cap_out * tanh_ex2(__uint_as_float(sv[i]) * p.cap_in));
+                }
                 if (!tile_full) {
 #pragma unroll
                     for (int i = 0; i < SC; ++i) {
@@ -748,6 +760,10 @@ attn_tc_pp_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
                 const int key0 = (t_begin + j) * BNK;
                 const int hi_col = valid ? pos - key0 : -1, lo_col = lo - key0;
                 const bool tile_full = __all_sync(0xffffffffu, valid && hi_col >= BNK - 1 && lo_col <= 0);
+                if (p.cap_in != 0.f) {
+#pragma unroll
+                    for (int i = 0; i < BNK; ++i) sv[i] = __float_as_uint(p.cap_out * tanh_ex2(__uint_as_float(sv[i]) * p.cap_in));
+                }
                 if (!tile_full) {
 #pragma unroll
                     for (int i = 0; i < BNK; ++i)
@@ -1137,7 +1153,7 @@ extern "C" int ttie_attn_tc_supported(int D, int page_size) {
 extern "C" int ttie_paged_attention_tc(const void* q, long long q_stride, const void* k_pages, const void* v_pages,
                                        int num_pages, const int* block_table, int table_width, int page_size, const int* qsl,
                                        const int* seq_lens, void* out, int T, int num_seqs, int Hq, int Hkv, int D,
-                                       int max_q_len, float scale, int window, int num_splits, int split_len, float* scratch,
+                                       int max_q_len, float scale, float softcap, int window, int num_splits, int split_len, float* scratch,
                                        int two_tiles, void* stream) {
     if (T <= 0 || num_seqs <= 0) return 0;
     if (!ttie_attn_tc_supported(D, page_size)) TTIE_FAIL("attention_tc: head size %d with pages of %d keys is not supported", D, page_size);
@@ -1159,6 +1175,7 @@ extern "C" int ttie_paged_attention_tc(const void* q, long long q_stride, const 
     p.q = (const __nv_bfloat16*)q; p.q_stride = q_stride; p.block_table = block_table; p.table_width = table_width;
     p.page_size = page_size; p.qsl = qsl; p.seq_lens = seq_lens; p.out = (__nv_bfloat16*)out;
     p.num_seqs = num_seqs; p.Hq = Hq; p.Hkv = Hkv; p.scale_log2 = scale * 1.4426950408889634f; p.window = window;
+    p.cap_in = softcap > 0.f ? scale / softcap : 0.f; p.cap_out = softcap > 0.f ? softcap / scale : 0.f;
     p.row_tiles = ceil_div(max_q_len * (Hq / Hkv), two_tiles && D <= 128 ? 2 * BM : BM);
     p.num_splits = num_splits; p.split_len = split_len;
     p.ws_o = scratch; p.ws_ml = scratch ? scratch + (size_t)T * Hq * num_splits * D : nullptr;

@@ -1,0 +1,176 @@
+// What lies between the q/k/v projection and the paged attention kernels for attention layers whose projections pass a short
+// causal convolution, whose rotation covers only the first `rot` values of a head, and whose value size differs from the
+// key size; and the per-head output gate behind the attention kernels.
+//
+//   qkv_conv_rope_store   one CTA per token.  The token's row [q | k | v] (Hq*D + Hkv*D + Hkv*Dv channels) is convolved over
+//                         time, y_t[c] = sum_k w[k][c] * u_(t - taps + 1 + k)[c] in 32-bit (weights tap-major; inputs before
+//                         the step's first token come from the request's state row, which holds the last taps - 1 projected
+//                         rows, oldest first, and is zero for a new request), q and k are rotated at the token's position
+//                         (pairs (i, i + rot/2) or (2i, 2i + 1); cos/sin from the step's table), q is written as
+//                         [T, Hq, Dp] and k, v into the pages [page, Hkv, slot, Dp]; Dp >= max(D, Dv), the rest zero.
+//   conv_tail_update      moves the step's last taps - 1 projected rows into the state rows (a request that brought fewer
+//                         keeps the newest of its old ones); runs after the kernel above has read the old rows.
+//   gate_head_rows        out[t, h, :Dv] = attn[t, h, :Dv] * sigmoid(gate[t, h]) (gate optional), dropping the padding.
+#include "common.cuh"
+using namespace ttie;
+
+namespace {
+
+__device__ __forceinline__ int slot_row_(int slot, int num_rows) { return slot < 0 ? num_rows - 1 : slot; }
+
+struct QkvArgs {
+    const void* proj; long long ld;
+    int Hq, Hkv, D, Dv, Dp;
+    int taps; const float* conv_w; const float* tail; int tail_rows;
+    const int* positions; const int* token_seq; const int* qsl; const int* slot_ids;
+    const float2* cs; int rot; int style;
+    void* q_out; void* k_pages; void* v_pages;
+    const int* block_table; int table_width, page_size, num_pages, write_kv;
+};
+
+// value i of a head row x after the rotation of its first `rot` values
+__device__ __forceinline__ float rotated(const float* x, int i, int rot, int style, const float2* cs) {
+    if (i >= rot) return x[i];
+    const int half = rot >> 1;
+    if (style == 1) {                                               // pairs (j, j + half)
+        if (i < half) { const float2 c = cs[i]; return x[i] * c.x - x[i + half] * c.y; }
+        const float2 c = cs[i - half];
+        return x[i] * c.x + x[i - half] * c.y;
+    }
+    const float2 c = cs[i >> 1];                                    // pairs (2j, 2j + 1)
+    return (i & 1) ? x[i] * c.x + x[i - 1] * c.y : x[i] * c.x - x[i + 1] * c.y;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) qkv_conv_rope_store_kernel(const QkvArgs a) {
+    TTIE_PDL_ENTRY();
+    extern __shared__ float row[];                                  // the token's convolved [q | k | v]
+    const int t = blockIdx.x;
+    const int C = a.Hq * a.D + a.Hkv * a.D + a.Hkv * a.Dv;
+    const T* proj = reinterpret_cast<const T*>(a.proj);
+    const int s = a.token_seq[t];
+    const int j = t - a.qsl[s];                                     // index among the request's tokens of this step
+    if (a.taps > 1) {
+        const float* tail = a.tail + (size_t)slot_row_(a.slot_ids[s], a.tail_rows) * (a.taps - 1) * C;
+        for (int c = threadIdx.x; c < C; c += blockDim.x) {
+            float acc = 0.f;
+            for (int k = 0; k < a.taps; ++k) {
+                const int src = j - (a.taps - 1) + k;
+                const float u = src >= 0 ? to_f32(proj[(size_t)(t - j + src) * a.ld + c]) : tail[(size_t)(a.taps - 1 + src) * C + c];
+                acc = fmaf(a.conv_w[(size_t)k * C + c], u, acc);
+            }
+            row[c] = acc;
+        }
+    } else {
+        for (int c = threadIdx.x; c < C; c += blockDim.x) {
+            const float u = to_f32(proj[(size_t)t * a.ld + c]);
+            row[c] = a.conv_w ? a.conv_w[c] * u : u;
+        }
+    }
+    __syncthreads();
+    const float2* cs = a.rot > 0 ? a.cs + (size_t)t * (a.rot >> 1) : nullptr;
+    T* q = reinterpret_cast<T*>(a.q_out) + (size_t)t * a.Hq * a.Dp;
+    for (int e = threadIdx.x; e < a.Hq * a.Dp; e += blockDim.x) {
+        const int h = e / a.Dp, i = e - h * a.Dp;
+        q[e] = from_f32<T>(i < a.D ? rotated(row + h * a.D, i, a.rot, a.style, cs) : 0.f);
+    }
+    if (!a.write_kv) return;
+    const int pos = a.positions[t];
+    int page = a.block_table[(size_t)s * a.table_width + pos / a.page_size];
+    if (page < 0 || page >= a.num_pages) page = 0;                  // validated on the host; never write outside
+    const int off = pos % a.page_size;
+    T* kp = reinterpret_cast<T*>(a.k_pages);
+    T* vp = reinterpret_cast<T*>(a.v_pages);
+    const float* krow = row + a.Hq * a.D;
+    const float* vrow = krow + a.Hkv * a.D;
+    for (int e = threadIdx.x; e < a.Hkv * a.Dp; e += blockDim.x) {
+        const int h = e / a.Dp, i = e - h * a.Dp;
+        const size_t dst = (((size_t)page * a.Hkv + h) * a.page_size + off) * a.Dp + i;
+        kp[dst] = from_f32<T>(i < a.D ? rotated(krow + h * a.D, i, a.rot, a.style, cs) : 0.f);
+        vp[dst] = from_f32<T>(i < a.Dv ? vrow[h * a.Dv + i] : 0.f);
+    }
+}
+
+template <typename T>
+__global__ void conv_tail_update_kernel(const T* __restrict__ proj, long long ld, int C, int taps, float* __restrict__ tail,
+                                        int tail_rows, const int* __restrict__ qsl, const int* __restrict__ slot_ids) {
+    TTIE_PDL_ENTRY();
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    const int s = blockIdx.y;
+    const int t0 = qsl[s], n = qsl[s + 1] - t0;
+    float* mine = tail + (size_t)slot_row_(slot_ids[s], tail_rows) * (taps - 1) * C + c;
+    for (int i = 0; i < taps - 1; ++i) {                            // ascending: row i takes from an old row behind it, or from the step
+        const int idx = n - (taps - 1) + i;
+        mine[(size_t)i * C] = idx >= 0 ? to_f32(proj[(size_t)(t0 + idx) * ld + c]) : mine[(size_t)(taps - 1 + idx) * C];
+    }
+}
+
+template <typename T>
+__global__ void gate_head_rows_kernel(const T* __restrict__ attn, const T* __restrict__ gate, long long ld_gate, int T_, int H, int Dv,
+                                      int Dp, T* __restrict__ out) {
+    TTIE_PDL_ENTRY();
+    const int col = blockIdx.x * blockDim.x + threadIdx.x;           // grid: (columns of a token's output row, tokens)
+    if (col >= H * Dv) return;
+    const int h = col / Dv, j = col - h * Dv;
+    for (size_t t = blockIdx.y; t < (size_t)T_; t += gridDim.y) {
+        float v = to_f32(attn[(t * H + h) * Dp + j]);
+        if (gate) v *= 1.0f / (1.0f + expf(-to_f32(gate[t * ld_gate + h])));
+        out[t * H * Dv + col] = from_f32<T>(v);
+    }
+}
+
+}  // namespace
+
+extern "C" int ttie_qkv_conv_rope_store(const void* proj, long long ld, int T, int Hq, int Hkv, int D, int Dv, int Dp, int taps,
+                                        const float* conv_w, const float* tail, int tail_rows, const int* positions,
+                                        const int* token_seq, const int* qsl, const int* slot_ids, const void* cs, int rot, int style,
+                                        void* q_out, void* k_pages, void* v_pages, const int* block_table, int table_width,
+                                        int page_size, int num_pages, int write_kv, int dtype, void* stream) {
+    if (T <= 0) return 0;
+    if (Dp < D || Dp < Dv) TTIE_FAIL("qkv_conv_rope_store: padded head size %d below %d / %d", Dp, D, Dv);
+    if (rot < 0 || rot > D || rot % 2) TTIE_FAIL("qkv_conv_rope_store: %d rotated values of a head of %d", rot, D);
+    if (rot > 0 && !cs) TTIE_FAIL("qkv_conv_rope_store: a rotation needs the step's cos/sin table");
+    if (taps < 1 || (taps > 1 && (!conv_w || !tail))) TTIE_FAIL("qkv_conv_rope_store: %d taps need weights and state rows", taps);
+    QkvArgs a;
+    a.proj = proj; a.ld = ld; a.Hq = Hq; a.Hkv = Hkv; a.D = D; a.Dv = Dv; a.Dp = Dp; a.taps = taps; a.conv_w = conv_w; a.tail = tail;
+    a.tail_rows = tail_rows; a.positions = positions; a.token_seq = token_seq; a.qsl = qsl; a.slot_ids = slot_ids;
+    a.cs = (const float2*)cs; a.rot = rot; a.style = style; a.q_out = q_out; a.k_pages = k_pages; a.v_pages = v_pages;
+    a.block_table = block_table; a.table_width = table_width; a.page_size = page_size; a.num_pages = num_pages; a.write_kv = write_kv;
+    const size_t smem = (size_t)(Hq * D + Hkv * D + Hkv * Dv) * sizeof(float);
+    if (smem > 200 * 1024) TTIE_FAIL("qkv_conv_rope_store: a row of %zu bytes exceeds shared memory", smem);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == kF32) {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(qkv_conv_rope_store_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        TTIE_LAUNCH(qkv_conv_rope_store_kernel<float>, T, 256, smem, s, a);
+    } else if (dtype == kBF16) {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(qkv_conv_rope_store_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        TTIE_LAUNCH(qkv_conv_rope_store_kernel<__nv_bfloat16>, T, 256, smem, s, a);
+    } else TTIE_FAIL("qkv_conv_rope_store: unknown dtype %d", dtype);
+    TTIE_CHECK_LAUNCH("qkv_conv_rope_store");
+    return 0;
+}
+
+extern "C" int ttie_conv_tail_update(const void* proj, long long ld, int C, int taps, float* tail, int tail_rows, const int* qsl,
+                                     const int* slot_ids, int num_seqs, int dtype, void* stream) {
+    if (num_seqs <= 0 || taps <= 1) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    dim3 grid(ceil_div(C, 256), num_seqs);
+    if (dtype == kF32) TTIE_LAUNCH(conv_tail_update_kernel<float>, grid, 256, 0, s, (const float*)proj, ld, C, taps, tail, tail_rows, qsl, slot_ids);
+    else if (dtype == kBF16) TTIE_LAUNCH(conv_tail_update_kernel<__nv_bfloat16>, grid, 256, 0, s, (const __nv_bfloat16*)proj, ld, C, taps, tail, tail_rows, qsl, slot_ids);
+    else TTIE_FAIL("conv_tail_update: unknown dtype %d", dtype);
+    TTIE_CHECK_LAUNCH("conv_tail_update");
+    return 0;
+}
+
+extern "C" int ttie_gate_head_rows(const void* attn, const void* gate, long long ld_gate, int T, int H, int Dv, int Dp, void* out,
+                                   int dtype, void* stream) {
+    if (T <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    dim3 grid(ceil_div(H * Dv, 256), T < 65535 ? T : 65535);
+    if (dtype == kF32) TTIE_LAUNCH(gate_head_rows_kernel<float>, grid, 256, 0, s, (const float*)attn, (const float*)gate, ld_gate, T, H, Dv, Dp, (float*)out);
+    else if (dtype == kBF16) TTIE_LAUNCH(gate_head_rows_kernel<__nv_bfloat16>, grid, 256, 0, s, (const __nv_bfloat16*)attn, (const __nv_bfloat16*)gate, ld_gate, T, H, Dv, Dp, (__nv_bfloat16*)out);
+    else TTIE_FAIL("gate_head_rows: unknown dtype %d", dtype);
+    TTIE_CHECK_LAUNCH("gate_head_rows");
+    return 0;
+}

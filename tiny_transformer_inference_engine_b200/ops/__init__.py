@@ -42,16 +42,16 @@ _SIGNATURES = {
                         _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void],
     "ttie_gemm_f32": [_c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void],
     "ttie_paged_attention": [_c_void, _c_ll, _c_void, _c_void, _c_void, _c_int, _c_int, _c_void, _c_void, _c_void,
-                             _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_int,
+                             _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_float, _c_int, _c_int, _c_int,
                              _c_void, _c_int, _c_void],
     "ttie_paged_attention_mma": [_c_void, _c_ll, _c_void, _c_void, _c_void, _c_int, _c_int, _c_void, _c_void, _c_void,
-                                 _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_int,
+                                 _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_float, _c_int, _c_int, _c_int,
                                  _c_void, _c_void],
     "ttie_paged_attention_mma_form": [_c_void, _c_ll, _c_void, _c_void, _c_void, _c_int, _c_int, _c_void, _c_void, _c_void,
-                                      _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_int,
+                                      _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_float, _c_int, _c_int, _c_int,
                                       _c_void, _c_int, _c_void],
     "ttie_paged_attention_tc": [_c_void, _c_ll, _c_void, _c_void, _c_int, _c_void, _c_int, _c_int, _c_void, _c_void, _c_void,
-                                _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_int, _c_void, _c_int,
+                                _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_float, _c_int, _c_int, _c_int, _c_void, _c_int,
                                 _c_void],
     "ttie_gemm_tc": [_c_void, _c_ll, _c_void, _c_ll, _c_void, _c_void, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void],
     "ttie_gemm_tc_pair": [_c_void, _c_ll, _c_void, _c_ll, _c_void, _c_void, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void],
@@ -76,6 +76,20 @@ _SIGNATURES = {
     "ttie_skinny_gemm_glu": [_c_void, _c_ll, _c_void, _c_ll, _c_void, _c_ll, _c_int, _c_int, _c_int, _c_float, _c_float, _c_float, _c_void],
     "ttie_gather_rows": [_c_void, _c_ll, _c_void, _c_int, _c_int, _c_int, _c_void, _c_int, _c_void],
     "ttie_moe_combine": [_c_void, _c_int, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_void, _c_int, _c_void],
+    "ttie_qkv_conv_rope_store": [_c_void, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void, _c_void, _c_int, _c_void,
+                                 _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int,
+                                 _c_int, _c_int, _c_int, _c_void],
+    "ttie_conv_tail_update": [_c_void, _c_ll, _c_int, _c_int, _c_void, _c_int, _c_void, _c_void, _c_int, _c_int, _c_void],
+    "ttie_gate_head_rows": [_c_void, _c_void, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_void, _c_int, _c_void],
+    "ttie_token_shift_mix": [_c_void, _c_ll, _c_int, _c_int, _c_int, _c_void, _c_void, _c_int, _c_void, _c_void, _c_void, _c_void, _c_int,
+                             _c_void],
+    "ttie_wkv_scan": [_c_void, _c_void, _c_void, _c_ll, _c_void, _c_ll, _c_void, _c_void, _c_void, _c_int, _c_void, _c_ll, _c_int, _c_void,
+                      _c_int, _c_void, _c_void, _c_int, _c_void, _c_int, _c_int, _c_int, _c_void],
+    "ttie_mlstm_scan": [_c_void, _c_void, _c_void, _c_ll, _c_void, _c_ll, _c_void, _c_void, _c_void, _c_int, _c_void, _c_void, _c_int,
+                        _c_void, _c_int, _c_int, _c_int, _c_float, _c_float, _c_int, _c_void],
+    "ttie_head_norm_gate": [_c_void, _c_void, _c_ll, _c_void, _c_int, _c_int, _c_int, _c_float, _c_int, _c_void, _c_int, _c_void],
+    "ttie_activation": [_c_void, _c_void, _c_ll, _c_int, _c_float, _c_int, _c_int, _c_void],
+    "ttie_matrix_state_pad": [_c_int],
     "ttie_sample": [_c_void, _c_int, _c_int, _c_void, _c_void, _c_void, _c_void, _c_void],
     "ttie_sample_tuned": [_c_void, _c_int, _c_int, _c_void, _c_void, _c_void, _c_void, _c_int, _c_void],
 }
@@ -775,7 +789,10 @@ class CudaOps:
 
     def paged_attention(self, qkv, num_heads, num_kv_heads, head_dim, k_pages, v_pages, block_table, page_size,
                         query_start_loc, seq_lens, num_seqs, max_q_len, max_kv_len, scale, window, out,
-                        plan=None):
+                        plan=None, softcap=0.0):
+        """Causal attention of the step's query rows over the paged keys and values.  ``window`` > 0: a row at position p
+        sees keys p - window + 1 .. p.  ``softcap`` > 0: a score s (scale applied) becomes softcap * tanh(s / softcap)
+        before mask and softmax."""
         T = qkv.shape[0]
         if max_kv_len > block_table.shape[1] * page_size:
             raise KernelError(f"paged_attention: a block table of {block_table.shape[1]} pages of {page_size} keys cannot cover {max_kv_len} keys")
@@ -788,7 +805,7 @@ class CudaOps:
             self._check(self.lib.ttie_paged_attention_tc(
                 _ptr(qkv), qkv.stride(0), _ptr(k_pages), _ptr(v_pages), k_pages.shape[0], _ptr(block_table),
                 block_table.shape[1], page_size, _ptr(query_start_loc), _ptr(seq_lens), _ptr(out), T, num_seqs, num_heads,
-                num_kv_heads, head_dim, max_q_len, float(scale), int(window), num_splits, split_len, _ptr(scratch),
+                num_kv_heads, head_dim, max_q_len, float(scale), float(softcap or 0.0), int(window), num_splits, split_len, _ptr(scratch),
                 1 if kernel == "tcpp" else 0, self._stream(qkv)), "paged_attention_tc")
             self.launches += 2 if num_splits > 1 else 1
             return
@@ -800,7 +817,7 @@ class CudaOps:
             self._check(self.lib.ttie_paged_attention_mma_form(
                 _ptr(qkv), qkv.stride(0), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
                 page_size, _ptr(query_start_loc), _ptr(seq_lens), _ptr(out), T, num_seqs, num_heads, num_kv_heads,
-                head_dim, max_q_len, float(scale), int(window), num_splits, split_len, _ptr(scratch),
+                head_dim, max_q_len, float(scale), float(softcap or 0.0), int(window), num_splits, split_len, _ptr(scratch),
                 form, self._stream(qkv)), "paged_attention_mma")
             self.launches += 2 if (num_splits > 1 and not form) else 1
             return
@@ -808,7 +825,7 @@ class CudaOps:
             self._check(self.lib.ttie_paged_attention(
                 _ptr(qkv), qkv.stride(0), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
                 page_size, _ptr(query_start_loc), _ptr(seq_lens), _ptr(out), T, num_seqs, num_heads, num_kv_heads,
-                head_dim, max_q_len, float(scale), int(window), num_splits, split_len, _ptr(scratch),
+                head_dim, max_q_len, float(scale), float(softcap or 0.0), int(window), num_splits, split_len, _ptr(scratch),
                 self._dt(qkv), self._stream(qkv)), "paged_attention")
         self.launches += 2 if num_splits > 1 else 1
 
@@ -920,6 +937,125 @@ class CudaOps:
                                              self._dt(xin), self._stream(xin)), "rglru_scan")
         self.launches += 4 if ws is not None else 1
         return out
+
+    # ---- attention with a short convolution on its projections, partial rotation, another value size, gated heads
+    def qkv_conv_rope_store(self, proj, num_heads, num_kv_heads, head_dim, v_dim, padded_dim, taps, conv_w, tail, positions, token_seq,
+                            query_start_loc, slot_ids, cs_table, rot, style, k_pages, v_pages, block_table, page_size, write_kv):
+        """From a step's projected rows ``proj`` [T, >= Hq*D + Hkv*D + Hkv*Dv] (columns [q | k | v]): the short causal
+        convolution over time (``conv_w`` float32 tap-major [taps, channels]; ``tail`` float32 state rows
+        [slots + 1, taps - 1, channels] with each request's last projected rows; ``taps`` 1 and ``conv_w`` None: none), the
+        rotation of the first ``rot`` values of every q and k head (``style`` 0: pairs (2i, 2i+1), 1: pairs (i, i + rot/2);
+        ``cs_table`` from ``rope_table``), and the store of k and v into the pages, rows padded with zeros to
+        ``padded_dim``.  Returns q [T, Hq * padded_dim].  The state rows are advanced by ``conv_tail_update``."""
+        T = proj.shape[0]
+        q = torch.empty((T, num_heads * padded_dim), dtype=proj.dtype, device=proj.device)
+        self._check(self.lib.ttie_qkv_conv_rope_store(
+            _ptr(proj), proj.stride(0), T, num_heads, num_kv_heads, head_dim, v_dim, padded_dim, int(taps), _ptr(conv_w), _ptr(tail),
+            0 if tail is None else tail.shape[0], _ptr(positions), _ptr(token_seq), _ptr(query_start_loc), _ptr(slot_ids),
+            _ptr(cs_table), int(rot), int(style), _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
+            int(page_size), k_pages.shape[0], 1 if write_kv else 0, self._dt(proj), self._stream(proj)), "qkv_conv_rope_store")
+        self.launches += 1
+        return q
+
+    def conv_tail_update(self, proj, channels, taps, tail, query_start_loc, slot_ids, num_seqs):
+        """Moves the last ``taps - 1`` projected rows of every request of the step into its state row (oldest first)."""
+        if taps <= 1:
+            return
+        self._check(self.lib.ttie_conv_tail_update(_ptr(proj), proj.stride(0), int(channels), int(taps), _ptr(tail), tail.shape[0],
+                                                   _ptr(query_start_loc), _ptr(slot_ids), int(num_seqs), self._dt(proj),
+                                                   self._stream(proj)), "conv_tail_update")
+        self.launches += 1
+
+    def gate_head_rows(self, attn, gate, num_heads, v_dim, padded_dim):
+        """out[t, h, :v_dim] = attn[t, h, :v_dim] * sigmoid(gate[t, h]); attn [T, H * padded_dim], gate a view [T, H] with a row
+        stride, or None (then only the padding is dropped)."""
+        T = attn.shape[0]
+        out = torch.empty((T, num_heads * v_dim), dtype=attn.dtype, device=attn.device)
+        self._check(self.lib.ttie_gate_head_rows(_ptr(attn), _ptr(gate), 0 if gate is None else gate.stride(0), T, num_heads, v_dim,
+                                                 padded_dim, _ptr(out), self._dt(attn), self._stream(attn)), "gate_head_rows")
+        self.launches += 1
+        return out
+
+    # ---- recurrent layers with a matrix state per head
+    MATRIX_STATE_KEYS_PER_THREAD = 16
+
+    @classmethod
+    def matrix_state_pad(cls, dim: int) -> int:
+        """Key channels of a matrix-state row as the scan kernels lay it out: a power-of-two number of slices of 16."""
+        slices = 1
+        while slices * cls.MATRIX_STATE_KEYS_PER_THREAD < dim:
+            slices *= 2
+        return slices * cls.MATRIX_STATE_KEYS_PER_THREAD
+
+    def token_shift_mix(self, x, mu, prev, token_seq, query_start_loc, slot_ids):
+        """mixes[m, t] = x[t] + (x[t-1] - x[t]) * mu[m]; a request's first token of the step takes x[t-1] from its row of
+        ``prev`` (float32 [slots + 1, d]).  x [T, d], mu float32 [M, d] -> [M, T, d]."""
+        T, d = x.shape
+        M = mu.shape[0]
+        out = torch.empty((M, T, d), dtype=x.dtype, device=x.device)
+        self._check(self.lib.ttie_token_shift_mix(_ptr(x), x.stride(0), T, d, M, _ptr(mu), _ptr(prev), prev.shape[0], _ptr(token_seq),
+                                                  _ptr(query_start_loc), _ptr(slot_ids), _ptr(out), self._dt(x), self._stream(x)),
+                    "token_shift_mix")
+        self.launches += 1
+        return out
+
+    def wkv_scan(self, r, k, v, wlog, w0, u, state, x, prev, query_start_loc, slot_ids, num_seqs, num_heads, dim):
+        """The time mix's recurrence over the step's tokens from the state rows ``state`` [slots + 1, H, dim, padded dim]
+        (advanced in place): o_t = (S + diag(u) k v^T)^T r, then S <- diag(w) S + k v^T with w = exp(-exp(wlog + w0)).
+        r, k, v [T, H*dim] views with one row stride; wlog float32 [T, H*dim].  Also stores each request's last row of ``x``
+        into ``prev``.  Returns o float32 [T, H*dim]."""
+        T = r.shape[0]
+        out = torch.empty((T, num_heads * dim), dtype=torch.float32, device=r.device)
+        if not (r.stride(0) == k.stride(0) == v.stride(0)):
+            raise KernelError("wkv_scan: r, k and v must share a row stride")
+        self._check(self.lib.ttie_wkv_scan(_ptr(r), _ptr(k), _ptr(v), r.stride(0), _ptr(wlog), wlog.stride(0), _ptr(w0), _ptr(u),
+                                           _ptr(state), state.shape[0], _ptr(x), x.stride(0), x.shape[1], _ptr(prev), prev.shape[0],
+                                           _ptr(query_start_loc), _ptr(slot_ids), int(num_seqs), _ptr(out), num_heads, dim,
+                                           self._dt(r), self._stream(r)), "wkv_scan")
+        self.launches += 1
+        return out
+
+    def mlstm_scan(self, q, k, v, gates, S, n, m, query_start_loc, slot_ids, num_seqs, num_heads, dim, v_dim, q_scale, cap):
+        """The matrix memory's recurrence over the step's tokens from the state rows S [slots + 1, H, v_dim, padded dim],
+        n [slots + 1, H, padded dim], m [slots + 1, H] (advanced in place).  q, k [T, H*dim], v [T, H*v_dim]: views with one row
+        stride; ``gates`` float32 [T, 2H], input-gate pre-activations then the forget gate's.  Returns o float32 [T, H*v_dim]."""
+        T = q.shape[0]
+        out = torch.empty((T, num_heads * v_dim), dtype=torch.float32, device=q.device)
+        if not (q.stride(0) == k.stride(0) == v.stride(0)):
+            raise KernelError("mlstm_scan: q, k and v must share a row stride")
+        self._check(self.lib.ttie_mlstm_scan(_ptr(q), _ptr(k), _ptr(v), q.stride(0), _ptr(gates), gates.stride(0), _ptr(S), _ptr(n), _ptr(m),
+                                             S.shape[0], _ptr(query_start_loc), _ptr(slot_ids), int(num_seqs), _ptr(out), num_heads,
+                                             dim, v_dim, float(q_scale), float(cap), self._dt(q), self._stream(q)), "mlstm_scan")
+        self.launches += 1
+        return out
+
+    def head_norm_gate(self, o, gate, weight, num_heads, v_dim, eps, act):
+        """out = o / rms(o over each head) * weight * act(gate); o float32 [T, H*v_dim], gate a view [T, H*v_dim] with a row
+        stride, weight float32 [H*v_dim]; ``act``: "silu" or "sigmoid".  Returns the compute dtype of ``gate``."""
+        T = o.shape[0]
+        out = torch.empty((T, num_heads * v_dim), dtype=gate.dtype, device=o.device)
+        self._check(self.lib.ttie_head_norm_gate(_ptr(o), _ptr(gate), gate.stride(0), _ptr(weight), T, num_heads, v_dim, float(eps),
+                                                 {"silu": 0, "sigmoid": 1}[act], _ptr(out), self._dt(gate), self._stream(o)),
+                    "head_norm_gate")
+        self.launches += 1
+        return out
+
+    # ---- elementwise functions between products
+    _ACTIVATIONS = {"relu2": 0, "tanh": 1, "softcap": 2}
+
+    def activation(self, x, kind, out_dtype=None, c=0.0, inplace=False):
+        """f(x) elementwise in 32-bit: "relu2" (relu squared), "tanh", "softcap" (c * tanh(x / c)); x contiguous."""
+        if not x.is_contiguous():
+            raise KernelError("activation: the input must be contiguous")
+        out = x if inplace else torch.empty(x.shape, dtype=out_dtype or x.dtype, device=x.device)
+        self._check(self.lib.ttie_activation(_ptr(x), _ptr(out), x.numel(), self._ACTIVATIONS[kind], float(c), self._dt(x),
+                                             self._dt(out), self._stream(x)), "activation")
+        self.launches += 1
+        return out
+
+    def linear_act(self, x, w, act):
+        """act(x @ w.T) -> [M, N] in the compute dtype."""
+        return self.activation(self.linear(x, w, None), act, inplace=True)
 
     # ---- gated linear units and routed experts
     def glu(self, gate_up, hidden, alpha=1.0, limit=0.0, shift=0.0):

@@ -13,6 +13,17 @@ product feeds the rotate-and-store kernel.  ``window`` (keys ``pos-window+1..pos
 and ``page_size`` (a page size of this layer's own cache group) are parameters of the part; the reference's
 model has neither.  A run entry that reads
 another entry's cache (``shares_kv``) has no k/v projection and stores nothing.
+
+Further options, each with its constants as parameters (any of them selects the general step below):
+``v_head_dim`` (a value size other than the key size), ``conv_taps`` (a short causal convolution over time on every
+channel of q, k and v, directly behind the projection and before the rotation; weights ``<name><conv_suffix>``
+[channels, taps], tap ``taps - 1`` multiplies the current token; the last ``taps - 1`` projected rows of a request are
+kept in a state row), a position encoding that rotates only the first ``position.dim`` values of a head, ``softcap``
+(a score s becomes ``softcap * tanh(s / softcap)`` before mask and softmax), ``gated`` (head h's output is scaled by
+``sigmoid(W_g x)_h``, one number per head), ``qkv_bias`` (biases on q, k and v only).  The general step: one product
+``[W_q; W_k; W_v; W_g] x``; one kernel convolves, rotates, writes q and stores k and v - rows padded with zeros to
+``padded_dim``, a multiple of 16 that holds both sizes, so every attention kernel of the package applies; a second moves the
+convolution's inputs into the state row; attention; the gate kernel drops the padding; ``W_o``.
 """
 from __future__ import annotations
 
@@ -21,7 +32,7 @@ from typing import Dict, Optional
 
 import torch
 
-from .base import Mixer, ParamSpec, PartSpec, PagedKVNeed, PagedKVView, StepContext
+from .base import Mixer, ParamSpec, PartSpec, PagedKVNeed, FixedStateNeed, PagedKVView, StepContext
 from ..registry import register_part, build_part
 
 
@@ -30,7 +41,10 @@ class PagedAttention(Mixer):
     def __init__(self, prefix: str, d_model: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  position: PartSpec, bias: bool = False, window: Optional[int] = None,
                  scale: Optional[float] = None, shares_kv: bool = False,
-                 names: Optional[Dict[str, str]] = None, page_size: Optional[int] = None):
+                 names: Optional[Dict[str, str]] = None, page_size: Optional[int] = None,
+                 v_head_dim: Optional[int] = None, conv_taps: Optional[int] = None, softcap: Optional[float] = None,
+                 gated: bool = False, qkv_bias: bool = False, weight_suffix: str = ".weight", bias_suffix: str = ".bias",
+                 conv_suffix: str = ".conv"):
         super().__init__(prefix)
         if num_heads % num_kv_heads:
             raise ValueError(f"num_heads={num_heads} is not a multiple of num_kv_heads={num_kv_heads}")
@@ -41,16 +55,37 @@ class PagedAttention(Mixer):
         self.page_size = None if page_size is None else int(page_size)     # None: the engine's page size
         self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(head_dim)
         self.position = build_part("position", position)
-        self.names = {"q": "q_proj", "k": "k_proj", "v": "v_proj", "o": "out"}
+        self.names = {"q": "q_proj", "k": "k_proj", "v": "v_proj", "o": "out", "g": "gate"}
         if names:
             self.names.update(names)
         self.w_in = self.b_in = self.w_out = self.b_out = None
+        self.v_head_dim = int(v_head_dim) if v_head_dim is not None else head_dim
+        self.conv_taps = int(conv_taps) if conv_taps else 1
+        if self.conv_taps < 1:
+            raise ValueError(f"conv_taps must be >= 1, got {conv_taps}")
+        self.softcap = float(softcap) if softcap else None
+        if self.softcap is not None and self.softcap <= 0:
+            raise ValueError(f"softcap must be positive or None, got {softcap}")
+        self.gated, self.qkv_bias = bool(gated), bool(qkv_bias)
+        self.weight_suffix, self.bias_suffix, self.conv_suffix = weight_suffix, bias_suffix, conv_suffix
+        self.rot_dim = int(getattr(self.position, "dim", 0) or 0)      # rotated values per head (0: none)
+        if self.rot_dim > head_dim:
+            raise ValueError(f"the position encoding rotates {self.rot_dim} values of a head of {head_dim}")
+        self.general = (self.v_head_dim != head_dim or self.conv_taps > 1 or self.gated or self.qkv_bias
+                        or self.rot_dim not in (0, head_dim))
+        if self.general and (self.shares_kv or self.bias):
+            raise ValueError("the general attention step has neither a shared cache nor an output bias")
+        self.padded_dim = -(-max(head_dim, self.v_head_dim) // 16) * 16 if self.general else head_dim
+        self.channels = (num_heads + num_kv_heads) * head_dim + num_kv_heads * self.v_head_dim      # of [q | k | v]
+        self.conv_w = None
 
     def children(self):
         return [self.position]
 
     # ---------------------------------------------------------------- tensors
     def param_specs(self):
+        if self.general:
+            return self._general_specs()
         n, d, D = self.names, self.d_model, self.head_dim
         specs = {f"{n['q']}.weight": ParamSpec((self.num_heads * D, d)),
                  f"{n['o']}.weight": ParamSpec((d, self.num_heads * D))}
@@ -63,7 +98,37 @@ class PagedAttention(Mixer):
                 specs[key.replace(".weight", ".bias")] = ParamSpec((w.shape[0],), storage="matrix", init="normal")
         return specs
 
+    def _general_specs(self):
+        n, d, D, Dv, ws = self.names, self.d_model, self.head_dim, self.v_head_dim, self.weight_suffix
+        rows = {"q": self.num_heads * D, "k": self.num_kv_heads * D, "v": self.num_kv_heads * Dv}
+        specs = {f"{n['o']}{ws}": ParamSpec((d, self.num_heads * Dv))}
+        for key, r in rows.items():
+            specs[f"{n[key]}{ws}"] = ParamSpec((r, d))
+            if self.qkv_bias:
+                specs[f"{n[key]}{self.bias_suffix}"] = ParamSpec((r,), storage="vector", init="normal")
+            if self.conv_taps > 1:
+                specs[f"{n[key]}{self.conv_suffix}"] = ParamSpec((r, self.conv_taps), storage="vector", init="normal", std=0.5)
+        if self.gated:
+            specs[f"{n['g']}{ws}"] = ParamSpec((self.num_heads, d))
+        return specs
+
+    def _general_load(self, params):
+        n, ws = self.names, self.weight_suffix
+        keys = ["q", "k", "v"] + (["g"] if self.gated else [])
+        self.w_in = torch.cat([params[f"{n[k]}{ws}"] for k in keys], dim=0).contiguous()
+        self.w_out = params[f"{n['o']}{ws}"].contiguous()
+        if self.qkv_bias:
+            b = [params[f"{n[k]}{self.bias_suffix}"].to(self.w_in.dtype) for k in ("q", "k", "v")]
+            if self.gated:
+                b.append(torch.zeros(self.num_heads, dtype=self.w_in.dtype, device=self.w_in.device))
+            self.b_in = torch.cat(b, dim=0).contiguous()
+        if self.conv_taps > 1:                                          # tap-major, 32-bit: a tap's weights lie side by side
+            w = torch.cat([params[f"{n[k]}{self.conv_suffix}"].float() for k in ("q", "k", "v")], dim=0)
+            self.conv_w = w.t().contiguous()
+
     def load(self, params):
+        if self.general:
+            return self._general_load(params)
         n = self.names
         keys = ["q"] if self.shares_kv else ["q", "k", "v"]
         self.w_in = torch.cat([params[f"{n[k]}.weight"] for k in keys], dim=0).contiguous()
@@ -78,14 +143,65 @@ class PagedAttention(Mixer):
     def validate(self, ops, dtype, page_size):
         check = getattr(ops, "check_attention", None)
         if check is not None:
-            check(dtype, self.num_heads, self.num_kv_heads, self.head_dim, self.page_size or page_size)
+            check(dtype, self.num_heads, self.num_kv_heads, self.padded_dim, self.page_size or page_size)
+        if self.general and self.channels * 4 > 200 * 1024:
+            raise ValueError(f"attention: {self.channels} q/k/v channels exceed what the convolve-rotate-store kernel stages")
 
     # ---------------------------------------------------------------- cache
-    def cache_need(self):
-        return PagedKVNeed(self.num_kv_heads, self.head_dim, self.window, self.page_size)
+    def cache_needs(self):
+        needs = [PagedKVNeed(self.num_kv_heads, self.padded_dim, self.window, self.page_size)]
+        if self.conv_taps > 1:
+            needs.append(FixedStateNeed((self.conv_taps - 1, self.channels), "float32"))
+        return needs
 
     # ---------------------------------------------------------------- step
-    def forward(self, x: torch.Tensor, ctx: StepContext, cache: PagedKVView) -> torch.Tensor:
+    def _general_forward(self, x, ctx, cache, tail):
+        ops = self.ops
+        Hq, Hkv, D, Dv, Dp, C = self.num_heads, self.num_kv_heads, self.head_dim, self.v_head_dim, self.padded_dim, self.channels
+        proj = ops.linear(x, self.w_in, self.b_in)                   # [T, channels (+ Hq gate columns)]
+        T = proj.shape[0]
+        table = self.position.rotary_table()
+        inv_freq, style = table if table is not None else (None, 0)
+        rot = self.rot_dim if inv_freq is not None else 0
+        cs = self.position.step_table(ctx) if rot else None
+        state = tail.state if tail is not None else None
+        q = ops.qkv_conv_rope_store(proj, Hq, Hkv, D, Dv, Dp, self.conv_taps, self.conv_w, state, ctx.positions, ctx.token_seq,
+                                    ctx.query_start_loc, ctx.slot_ids, cs, rot, style, cache.k_pages, cache.v_pages,
+                                    cache.block_table, cache.page_size, cache.writable)
+        if self.conv_taps > 1 and tail.writable:
+            ops.conv_tail_update(proj, C, self.conv_taps, state, ctx.query_start_loc, ctx.slot_ids, ctx.num_seqs)
+        out = torch.empty((T, Hq * Dp), dtype=x.dtype, device=x.device)
+        self._attend(q, Dp, ctx, cache, out)
+        if self.gated or Dp != Dv:
+            out = ops.gate_head_rows(out, proj[:, C:] if self.gated else None, Hq, Dv, Dp)
+        return ops.linear(out, self.w_out, None, partial_ok=True)
+
+    def _attend(self, q, D, ctx, cache, out):
+        """One attention launch per class of requests (decoded tokens; prompt portions), each planned as if it were alone."""
+        ops, Hq, Hkv = self.ops, self.num_heads, self.num_kv_heads
+        classes = ctx.classes()
+        if len(classes) == 1:
+            c = classes[0]
+            ops.paged_attention(q, Hq, Hkv, D, cache.k_pages, cache.v_pages, cache.block_table, cache.page_size,
+                                c.query_start_loc, ctx.seq_lens, ctx.num_seqs, c.max_q_len, c.max_kv_len,
+                                self.scale, self.window or 0, out, softcap=self.softcap or 0.0)
+            return
+        for ci, c in enumerate(classes):
+            key = ("attention class views", id(cache.block_table), ci)    # the same for every layer of a cache group
+            views = ctx.step_cache.get(key)
+            if views is None:
+                views = ctx.step_cache[key] = (cache.block_table[c.seq_lo:c.seq_hi], ctx.seq_lens[c.seq_lo:c.seq_hi])
+            ops.paged_attention(q[c.tok_lo:c.tok_hi], Hq, Hkv, D, cache.k_pages, cache.v_pages, views[0],
+                                cache.page_size, c.query_start_loc, views[1], c.seq_hi - c.seq_lo, c.max_q_len,
+                                c.max_kv_len, self.scale, self.window or 0, out[c.tok_lo:c.tok_hi], softcap=self.softcap or 0.0)
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache) -> torch.Tensor:
+        tail = None
+        if isinstance(cache, (list, tuple)):                         # the views in the order of cache_needs()
+            tail = cache[1] if len(cache) > 1 else None
+            cache = cache[0]
+        if self.general:
+            return self._general_forward(x, ctx, cache, tail)
         ops = self.ops
         Hq, Hkv, D = self.num_heads, self.num_kv_heads, self.head_dim
         write = cache.writable and not self.shares_kv
@@ -111,20 +227,5 @@ class PagedAttention(Mixer):
                        cache.k_pages, cache.v_pages, cache.block_table, cache.page_size, write,
                        q_out=q if qkv.dim() == 3 else None, cs_table=cs_table)
         out = torch.empty((T, Hq * D), dtype=x.dtype, device=x.device)
-        # one launch per class of requests (decoded tokens; prompt portions), each planned as if it were alone
-        classes = ctx.classes()
-        if len(classes) == 1:
-            c = classes[0]
-            ops.paged_attention(q, Hq, Hkv, D, cache.k_pages, cache.v_pages, cache.block_table, cache.page_size,
-                                c.query_start_loc, ctx.seq_lens, ctx.num_seqs, c.max_q_len, c.max_kv_len,
-                                self.scale, self.window or 0, out)
-        else:
-            for ci, c in enumerate(classes):
-                key = ("attention class views", id(cache.block_table), ci)    # the same for every layer of a cache group
-                views = ctx.step_cache.get(key)
-                if views is None:
-                    views = ctx.step_cache[key] = (cache.block_table[c.seq_lo:c.seq_hi], ctx.seq_lens[c.seq_lo:c.seq_hi])
-                ops.paged_attention(q[c.tok_lo:c.tok_hi], Hq, Hkv, D, cache.k_pages, cache.v_pages, views[0],
-                                    cache.page_size, c.query_start_loc, views[1], c.seq_hi - c.seq_lo, c.max_q_len,
-                                    c.max_kv_len, self.scale, self.window or 0, out[c.tok_lo:c.tok_hi])
+        self._attend(q, D, ctx, cache, out)
         return ops.linear(out, self.w_out, self.b_out, partial_ok=True)

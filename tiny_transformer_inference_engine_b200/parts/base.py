@@ -47,7 +47,8 @@ class ParamSpec:
     ``matrix`` tensors are cast to the compute dtype.  ``vector`` tensors that the
     file stores in 32-bit stay 32-bit (their kernels read either width); stored in
     16-bit they are widened only for a float32 run.  ``table`` tensors are integer
-    tables and are kept as int32.
+    tables and are kept as int32.  A size of -1 in ``shape`` is one that only the weight file knows (the
+    loader accepts any; the part reads it off the tensor in ``load``).
     """
     shape: Tuple[int, ...]
     storage: str = "matrix"            # "matrix" | "vector" | "table"

@@ -33,22 +33,30 @@ class TokenEmbedding(Embedding):
 
 @register_part("head", "linear")
 class LinearHead(Head):
-    def __init__(self, prefix: str, dim: int, vocab_size: int):
+    """``logits = W x``; with ``softcap`` c the logits leave as ``c * tanh(logits / c)``.  ``name``: the matrix's relative name."""
+
+    def __init__(self, prefix: str, dim: int, vocab_size: int, name: str = "weight", softcap=None):
         super().__init__(prefix)
-        self.dim, self.vocab_size = int(dim), int(vocab_size)
+        self.dim, self.vocab_size, self.name = int(dim), int(vocab_size), name
+        self.softcap = None if softcap is None else float(softcap)
+        if self.softcap is not None and not self.softcap > 0:
+            raise ValueError(f"softcap must be positive or None, got {softcap}")
         self.weight = None
 
     def param_specs(self):
-        return {"weight": ParamSpec((self.vocab_size, self.dim))}
+        return {self.name: ParamSpec((self.vocab_size, self.dim))}
 
     def load(self, params):
-        self.weight = params["weight"].contiguous()
+        self.weight = params[self.name].contiguous()
 
     def product_weights(self):
         return [self.weight]
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return self.ops.linear(x, self.weight, None, out_dtype=torch.float32)
+        logits = self.ops.linear(x, self.weight, None, out_dtype=torch.float32)
+        if self.softcap is not None:
+            self.ops.activation(logits, "softcap", c=self.softcap, inplace=True)
+        return logits
 
 
 @register_part("head", "tied")

@@ -82,3 +82,35 @@ class GLU(FeedForward):
     def forward(self, x: torch.Tensor, ctx: StepContext, partial_ok: bool = True) -> torch.Tensor:
         act = self.ops.linear_glu(x, self.w_gu, self.hidden, self.alpha, self.limit or 0.0, self.shift)
         return self.ops.linear(act, self.w_down, None, partial_ok=partial_ok)
+
+
+@register_part("ffn", "mlp")
+class MLP(FeedForward):
+    """A two-matrix feed-forward ``down(act(up(x)))`` without biases.  ``act``: ``"relu2"``, the square of relu.
+    ``names``: relative tensor names of the two matrices."""
+    ACTIVATIONS = ("relu2",)
+
+    def __init__(self, prefix: str, d_model: int, hidden: int, act: str = "relu2", names: Optional[Dict[str, str]] = None):
+        super().__init__(prefix)
+        if act not in self.ACTIVATIONS:
+            raise ValueError(f"unknown activation {act!r}; known: {self.ACTIVATIONS}")
+        self.d_model, self.hidden, self.act = int(d_model), int(hidden), act
+        self.names = {"up": "up", "down": "down"}
+        if names:
+            self.names.update(names)
+        self.w_up = self.w_down = None
+
+    def param_specs(self):
+        n, d, F = self.names, self.d_model, self.hidden
+        return {n["up"]: ParamSpec((F, d)), n["down"]: ParamSpec((d, F))}
+
+    def load(self, params):
+        self.w_up = params[self.names["up"]].contiguous()
+        self.w_down = params[self.names["down"]].contiguous()
+
+    def product_weights(self):
+        return [self.w_up, self.w_down]
+
+    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        act = self.ops.linear_act(x, self.w_up, self.act)             # [T, F]
+        return self.ops.linear(act, self.w_down, None, partial_ok=True)

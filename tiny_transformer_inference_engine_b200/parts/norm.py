@@ -18,17 +18,18 @@ from ..registry import register_part
 
 @register_part("norm", "rmsnorm")
 class RMSNorm(Norm):
-    def __init__(self, prefix: str, dim: int, eps: float):
+    def __init__(self, prefix: str, dim: int, eps: float, name: str = "weight"):
         super().__init__(prefix)
         self.dim = int(dim)
         self.eps = float(eps)
+        self.name = name                   # relative name of the weight tensor
         self.weight = None
 
     def param_specs(self) -> Dict[str, ParamSpec]:
-        return {"weight": ParamSpec((self.dim,), storage="vector", init="ones")}
+        return {self.name: ParamSpec((self.dim,), storage="vector", init="ones")}
 
     def load(self, params):
-        self.weight = params["weight"]
+        self.weight = params[self.name]
 
     def validate(self, ops, dtype, page_size):
         check = getattr(ops, "check_norm", None)

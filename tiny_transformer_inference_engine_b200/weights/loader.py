@@ -74,7 +74,7 @@ def place(stored: Dict[str, torch.Tensor], specs, compute_dtype: torch.dtype, de
             missing.append((name, ps.shape))
             continue
         t = stored[name]
-        if tuple(t.shape) != tuple(ps.shape):
+        if len(t.shape) != len(ps.shape) or any(e != -1 and g != e for g, e in zip(t.shape, ps.shape)):   # (-1: the file decides)
             wrong_shape.append((name, tuple(t.shape), tuple(ps.shape)))
         if ps.storage == "table":
             if t.dtype.is_floating_point:

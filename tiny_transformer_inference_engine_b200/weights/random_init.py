@@ -33,6 +33,9 @@ def random_tensors(config: ModelConfig, seed: int, std: float = 0.02, perturb_no
     specs = model.param_specs()
     for name in sorted(specs):
         ps = specs[name][2]
+        if any(n < 0 for n in ps.shape):
+            raise ValueError(f"tensor {name}: its shape {list(ps.shape)} leaves a size to the weight file; the configuration "
+                             "must name it before random weights can be drawn")
         if ps.storage == "table":
             # integer tables: uniform in [0, high), or 0, 1, 2, ... along the last dimension, or zeros
             if ps.init == "randint" and ps.high:
