@@ -280,6 +280,34 @@ def munevik_config(width, heads, layers=4):
             "max_seq_len": 4096}
 
 
+def mizupel_config(width, heads, layers=4):
+    """A Mizupel model at layer sizes that resemble a real model's: grouped-query attention with heads of 128 (eight query heads
+    per kv head), four convolution taps, 64 rotated values, a window of 1,024 keys and soft-capped scores; a matrix memory of
+    width / 128 heads with 64 key and 128 value channels; time mixing with heads of 64 and a decay path of rank 64; feed-forwards
+    of 4 x width.  Layer order: attention + feed-forward, matrix memory, time mixing + feed-forward, attention + feed-forward,
+    repeated."""
+    att = {"heads": heads, "kv_heads": max(1, heads // 8), "dim": 128, "vdim": 128, "conv": 4, "mask": {"size": 1024},
+           "rot": {"base": 10000.0, "dims": 64, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}},
+           "scale": 128 ** -0.5, "softcap": 50.0}
+    mem = {"heads": heads, "dim": 64, "vdim": 128, "gate_cap": 15.0}
+    mix = {"heads": width // 64, "dim": 64, "decay_rank": 64}
+    ff = {"kind": "dense", "ff": 4 * width}
+    out = []
+    for i in range(layers):
+        k = i % 4
+        if k in (0, 3):
+            out.append({"type": "attention", "mixer": dict(att), "mlp": ff})
+        elif k == 1:
+            out.append({"type": "mlstm", "mixer": dict(mem), "mlp": None})
+        else:
+            out.append({"type": "wkv", "mixer": dict(mix), "mlp": ff})
+    return {"architecture": "Mizupel", "vocab": 32000, "width": width, "norm": {"eps": 1e-6}, "logit_softcap": 30.0, "layers": out,
+            "max_seq_len": 4096}
+
+
+DESIGNS = {"munevik": ("Munevik", munevik_config, 1024), "mizupel": ("Mizupel", mizupel_config, 1024)}     # name, configuration, window
+
+
 def like_config(width, heads, layers=4):
     """The closest existing model at equal size: pre-norm multi-query attention blocks with heads of 128 and SwiGLU of 4 x width."""
     return dict(architecture="mqa_gpt", vocab_size=32000, d_model=width, num_layers=layers, num_heads=width // 128, num_kv_heads=1,
@@ -291,7 +319,9 @@ class OpRecorder:
     afterwards, and its algorithmic bytes and flops from the shapes."""
     NAMES = ("embed", "add_rmsnorm", "rmsnorm_rows", "linear", "linear_swiglu", "rope_table", "rope_store", "paged_attention",
              "scale_add_layernorm", "cast_rows", "latent_store", "latent_query", "gate_heads", "batched_linear", "causal_conv",
-             "rglru_scan", "glu", "linear_glu", "grouped_glu", "moe_route", "moe_plan", "grouped_linear", "moe_combine")
+             "rglru_scan", "glu", "linear_glu", "grouped_glu", "moe_route", "moe_plan", "grouped_linear", "moe_combine",
+             "qkv_conv_rope_store", "conv_tail_update", "gate_head_rows", "token_shift_mix", "wkv_scan", "mlstm_scan", "head_norm_gate",
+             "activation", "linear_act")
 
     def __init__(self, ops):
         self.ops, self.calls, self.orig, self.depth = ops, [], {}, 0
@@ -335,7 +365,26 @@ def op_cost(name, args, kw, out, kv_lens, window):
     """(bytes that must move, flops) of one recorded call, from its shapes."""
     import torch
     flops = 0
-    if name in ("linear", "linear_swiglu", "linear_glu"):
+    if name in ("wkv_scan", "mlstm_scan"):
+        # the step's rows in and out, each request's state row read and written once; the recurrence's arithmetic is 32-bit on
+        # the ordinary cores: three (wkv) or four (mlstm) multiply-adds per state element and token, returned as a second count
+        if name == "wkv_scan":
+            r, state, n, H, D = args[0], args[6], args[11], args[12], args[13]
+            T, per_tok, fma = r.shape[0], 3 * H * D * r.element_size() + 8 * H * D, 3 * H * D * D
+        else:
+            q, state, n, H, D, Dv = args[0], args[4], args[9], args[10], args[11], args[12]
+            T, per_tok, fma = q.shape[0], (2 * H * D + H * Dv) * q.element_size() + 4 * H * Dv + 8 * H, 4 * H * D * Dv
+        row = state[0].numel() * 4
+        return T * per_tok + 2 * n * row, ("fp32", 2 * T * fma)
+    if name == "qkv_conv_rope_store":                              # pages and state rows are pools: count the rows read and written
+        return 2 * _tensor_bytes(args[0]) + _tensor_bytes(out), 0
+    if name == "conv_tail_update":                                 # (proj, channels, taps, tail, qsl, slots, requests)
+        return 2 * args[6] * (args[2] - 1) * args[1] * 4, 0
+    if name == "token_shift_mix":
+        return _tensor_bytes([args[0], out]), 0
+    if name in ("head_norm_gate", "gate_head_rows"):
+        return _tensor_bytes([args[0], args[1], out]), 0
+    if name in ("linear", "linear_swiglu", "linear_glu", "linear_act"):
         x, w = args[0], args[1]
         flops = 2 * x.shape[0] * w.shape[0] * w.shape[1]
         return _tensor_bytes([x, w, out]), flops
@@ -365,6 +414,9 @@ def op_cost(name, args, kw, out, kv_lens, window):
     return _tensor_bytes(tensors) + _tensor_bytes(out) - skip, 0
 
 
+FP32_NOMINAL_FLOPS = 148 * 128 * 2 * 1.965e9        # 148 SMs x 128 lanes x one multiply-add per clock at the highest SM clock (nominal, not measured)
+
+
 def time_ops(eng, entries_fn, pk, kv_lens, window, iters=8):
     """Runs one step with every operation recorded, then times each recorded call alone (a replayed graph of ``iters`` calls);
     returns rows (operation, calls, microseconds, fraction of its roofline)."""
@@ -380,9 +432,12 @@ def time_ops(eng, entries_fn, pk, kv_lens, window, iters=8):
             torch.cuda.synchronize()
             us = timed(lambda i: fn(*args, **kw), iters) * 1e3 / iters
         b, f = op_cost(name, args, kw, out, kv_lens, window)
-        ideal = max(b / (pk["hbm_gbs"] * 1e9), f / (pk["bf16_tflops"] * 1e12)) * 1e6
+        if isinstance(f, tuple):                                  # 32-bit arithmetic on the ordinary cores: against their nominal rate
+            ideal = max(b / (pk["hbm_gbs"] * 1e9), f[1] / FP32_NOMINAL_FLOPS) * 1e6
+        else:
+            ideal = max(b / (pk["hbm_gbs"] * 1e9), f / (pk["bf16_tflops"] * 1e12)) * 1e6
         key = name
-        if name in ("linear", "batched_linear", "grouped_linear", "linear_swiglu", "linear_glu", "grouped_glu"):
+        if name in ("linear", "batched_linear", "grouped_linear", "linear_swiglu", "linear_glu", "grouped_glu", "linear_act"):
             w = args[1]
             key = f"{name} {list(w.shape)}"
         r = rows.setdefault(key, {"calls": 0, "us": 0.0, "ideal_us": 0.0})
@@ -394,8 +449,8 @@ def time_ops(eng, entries_fn, pk, kv_lens, window, iters=8):
 
 
 def run_design(args, pk):
-    """Prefill and decode throughput of the Munevik design at a few sizes, beside the closest existing model (multi-query GPT)
-    at equal width and depth, with every operation of a step timed alone against its roofline."""
+    """Prefill and decode throughput of a design (``--design``) at a few sizes, beside the closest existing model (multi-query
+    GPT) at equal width and depth, with every operation of a step timed alone against its roofline."""
     import torch
     from tiny_transformer_inference_engine_b200 import Engine, ModelConfig, EngineConfig, CacheConfig, SchedulerConfig, StepEntry, SamplingParams
     from tiny_transformer_inference_engine_b200.weights import random_tensors
@@ -403,7 +458,8 @@ def run_design(args, pk):
     Tp, batch, ctx, K, W = 2048, args.batch, 2048, args.steps, max(args.warmup, 3)
     report = {}
     for width, heads in sizes:
-        for label, cfg in (("munevik", munevik_config(width, heads, args.layers or 4)), ("mqa_gpt", like_config(width, heads, args.layers or 4))):
+        design_name, design_config, design_window = DESIGNS[args.design]
+        for label, cfg in ((args.design, design_config(width, heads, args.layers or 4)), ("mqa_gpt", like_config(width, heads, args.layers or 4))):
             mc = ModelConfig.from_dict(cfg)
             page = 64
             pages = batch * (ctx // page + 4) + Tp // page + 8
@@ -426,7 +482,7 @@ def run_design(args, pk):
             for _ in range(3):
                 prefill_once()
             p_ms = timed(prefill_once, 5) / 5
-            window = 1024 if label == "munevik" else 0
+            window = design_window if label == args.design else 0
             saved_cap, eng.stepper.capture_repeated = eng.stepper.capture_repeated, False     # the recorded step runs eagerly
             p_ops = time_ops(eng, prefill_once, pk, [(Tp, Tp)], window)
             eng.stepper.capture_repeated = saved_cap
@@ -450,11 +506,11 @@ def run_design(args, pk):
             report[f"{label}_{width}"] = {
                 "prefill_tokens_per_s": round(Tp / (p_ms / 1e3)), "prefill_ms": round(p_ms, 3),
                 "decode_tokens_per_s": round(batch * K / (ms / 1e3)), "decode_ms_per_step": round(ms / K, 4),
-                "decode_launches_per_step": launches // K, "layers": len(mc.layers) if label == "munevik" else mc.num_layers,
+                "decode_launches_per_step": launches // K, "layers": len(mc.layers) if label == args.design else mc.num_layers,
                 "prefill_ops": p_ops, "decode_ops": d_ops}
             del eng
             torch.cuda.empty_cache()
-    print(json.dumps({"design": "Munevik", "beside": "mqa_gpt", "dtype": "bf16", "data": "synthetic token ids, random-init weights",
+    print(json.dumps({"design": DESIGNS[args.design][0], "beside": "mqa_gpt", "dtype": "bf16", "data": "synthetic token ids, random-init weights",
                       "prefill_tokens": Tp, "decode_batch": batch, "decode_context": ctx, "steps": K, "warmup": W,
                       "peaks": pk, "sizes": report}))
     return 0
@@ -462,7 +518,7 @@ def run_design(args, pk):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--design", default=None, choices=("munevik",), help="prefill and decode of this design at a few sizes beside the closest existing model, with per-operation times")
+    ap.add_argument("--design", default=None, choices=("munevik", "mizupel"), help="prefill and decode of this design at a few sizes beside the closest existing model, with per-operation times")
     ap.add_argument("--sizes", default=None, help="with --design: comma-separated model widths (multiples of 128)")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)

@@ -161,7 +161,8 @@ def test_rope_store(ops, dtype, Hq, Hkv, D, page, style, base):
 
 
 # ------------------------------------------------------------------------------------------ attention
-def attention_case(ops, dtype, Hq, Hkv, D, page, seqs, window=0, plan=None, seed=0, spike=None, split_at=None, plans_seen=None):
+def attention_case(ops, dtype, Hq, Hkv, D, page, seqs, window=0, plan=None, seed=0, spike=None, split_at=None, plans_seen=None,
+                   softcap=0.0):
     """seqs: list of (kv_len, q_len).  spike=(seq, query index, key position): that query and that
     key are made parallel and large so the key decides the row's output.  split_at: the first
     ``split_at`` requests and the others run as two launches over views of the same step, as the
@@ -202,7 +203,7 @@ def attention_case(ops, dtype, Hq, Hkv, D, page, seqs, window=0, plan=None, seed
     max_q, max_kv = max(n for _, n in seqs), max(L for L, _ in seqs)
     if split_at is None:
         ops.paged_attention(qkv.to(DEV), Hq, Hkv, D, kp.to(DEV), vp.to(DEV), table.to(DEV), page, qsl_t.to(DEV),
-                            seq_lens.to(DEV), N, max_q, max_kv, scale, window, out, plan=plan)
+                            seq_lens.to(DEV), N, max_q, max_kv, scale, window, out, plan=plan, softcap=softcap)
     else:
         q_d, kp_d, vp_d, table_d, lens_d = qkv.to(DEV), kp.to(DEV), vp.to(DEV), table.to(DEV), seq_lens.to(DEV)
         for lo, hi in ((0, split_at), (split_at, N)):
@@ -211,7 +212,7 @@ def attention_case(ops, dtype, Hq, Hkv, D, page, seqs, window=0, plan=None, seed
             if plans_seen is not None:
                 plans_seen.append(ops.attention_plan(dt, hi - lo, Hq, Hkv, D, mq, mk, page))
             ops.paged_attention(q_d[t0:t1], Hq, Hkv, D, kp_d, vp_d, table_d[lo:hi], page, (qsl_t[lo:hi + 1] - t0).to(DEV),
-                                lens_d[lo:hi], hi - lo, mq, mk, scale, window, out[t0:t1], plan=plan)
+                                lens_d[lo:hi], hi - lo, mq, mk, scale, window, out[t0:t1], plan=plan, softcap=softcap)
     exp = torch.empty(T, Hq * D)
     G = Hq // Hkv
     for i, (L, n) in enumerate(seqs):
@@ -223,6 +224,8 @@ def attention_case(ops, dtype, Hq, Hkv, D, page, seqs, window=0, plan=None, seed
             vis = vis & (kpos > qpos - window)
         for h in range(Hq):
             s = (q[:, h] @ k[:, h // G].T) * scale
+            if softcap:
+                s = softcap * torch.tanh(s / softcap)
             p = torch.softmax(s.masked_fill(~vis, float("-inf")), -1)
             exp[qsl[i]:qsl[i + 1], h * D:(h + 1) * D] = p @ v[:, h // G]
     return out.float().cpu(), exp, dense, qsl
@@ -932,3 +935,30 @@ def test_tcgen05_attention_refuses(ops):
         attention_case(ops, "bfloat16", 4, 1, 64, 24, [(40, 40)], plan=("tc", 1, 0))
     with pytest.raises(KernelError, match="prompt-portion form only"):
         attention_case(ops, "bfloat16", 4, 1, 256, 16, [(40, 40)], plan=("tc", 1, 0))
+
+
+# ------------------------------------------------------------------------------------------ score soft cap
+@pytest.mark.parametrize("dtype,plan,seqs,spike", [
+    ("float32", ("simt", 1, 0), [(77, 77), (300, 1), (129, 2)], (0, 40, 20)),
+    ("float32", ("simt", 3, 128), [(300, 1), (129, 2), (260, 40)], (0, 0, 250)),
+    ("bfloat16", ("simt", 1, 0), [(77, 77), (300, 1), (129, 2)], (0, 40, 20)),
+    ("bfloat16", ("mma", 1, 0), [(77, 77), (300, 1), (129, 2), (200, 150)], (0, 40, 20)),
+    ("bfloat16", ("mma", 3, 128), [(300, 1), (129, 2), (260, 40)], (0, 0, 250)),
+    ("bfloat16", ("mma_c4", 4, 128), [(300, 1), (129, 1), (420, 1)], (0, 0, 250)),
+    ("bfloat16", ("mma_c2", 2, 256), [(300, 1), (129, 1), (420, 1)], (0, 0, 250)),
+    ("bfloat16", ("tc", 1, 0), [(300, 64), (130, 130), (500, 1)], (0, 3, 200)),
+    ("bfloat16", ("tc", 4, 128), [(300, 64), (130, 130), (500, 1)], (0, 3, 200)),
+    ("bfloat16", ("tcpp", 1, 0), [(300, 64), (130, 130), (500, 1)], (0, 3, 200)),
+    ("bfloat16", ("tcpp", 2, 256), [(300, 64), (130, 130), (500, 1)], (0, 3, 200)),
+])
+def test_score_softcap_in_every_attention_kernel(ops, dtype, plan, seqs, spike):
+    """cap * tanh(score / cap) before mask and softmax, with scores well beyond the cap (a query and a key made parallel and
+    large): without the cap the spiked key would take the whole row; with it the row stays a mixture.  Every kernel and its
+    cut form against the float32 reference, with a window."""
+    Hq, Hkv, D, page, cap = 8, 2, 64, 16, 1.0
+    out, exp, dense, qsl = attention_case(ops, dtype, Hq, Hkv, D, page, seqs, plan=plan, spike=spike, softcap=cap, window=190)
+    assert torch.isfinite(out).all()
+    assert rel(out, exp) < TOL[dtype]
+    uncapped, exp_uncapped, _, _ = attention_case(ops, dtype, Hq, Hkv, D, page, seqs, plan=plan, spike=spike, window=190)
+    assert rel(uncapped, exp_uncapped) < TOL[dtype]
+    assert (exp - exp_uncapped).abs().max() > 0.05                          # the cap is what the comparison above rests on

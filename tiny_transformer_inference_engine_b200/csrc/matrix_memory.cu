@@ -307,6 +307,10 @@ extern "C" int ttie_wkv_scan(const void* r, const void* k, const void* v, long l
     const size_t smem = (size_t)TB * (3 * a.Dpad + cols) * sizeof(float);
     dim3 grid(ceil_div(D, cols), H, num_seqs);
     cudaStream_t s = (cudaStream_t)stream;
+    if (smem > 48 * 1024) {                                          // (wide heads: more staging than a kernel gets unasked)
+        cudaFuncSetAttribute(wkv_scan_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaFuncSetAttribute(wkv_scan_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    }
     if (dtype == kF32) TTIE_LAUNCH(wkv_scan_kernel<float>, grid, threads, smem, s, a);
     else if (dtype == kBF16) TTIE_LAUNCH(wkv_scan_kernel<__nv_bfloat16>, grid, threads, smem, s, a);
     else TTIE_FAIL("wkv_scan: unknown dtype %d", dtype);
@@ -328,6 +332,10 @@ extern "C" int ttie_mlstm_scan(const void* q, const void* k, const void* v, long
     const size_t smem = (size_t)TB * (2 * a.Dpad + cols + 3) * sizeof(float);
     dim3 grid(ceil_div(Dv, cols), H, num_seqs);
     cudaStream_t s = (cudaStream_t)stream;
+    if (smem > 48 * 1024) {
+        cudaFuncSetAttribute(mlstm_scan_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaFuncSetAttribute(mlstm_scan_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    }
     if (dtype == kF32) TTIE_LAUNCH(mlstm_scan_kernel<float>, grid, threads, smem, s, a);
     else if (dtype == kBF16) TTIE_LAUNCH(mlstm_scan_kernel<__nv_bfloat16>, grid, threads, smem, s, a);
     else TTIE_FAIL("mlstm_scan: unknown dtype %d", dtype);

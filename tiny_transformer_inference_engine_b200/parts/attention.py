@@ -60,9 +60,10 @@ class PagedAttention(Mixer):
             self.names.update(names)
         self.w_in = self.b_in = self.w_out = self.b_out = None
         self.v_head_dim = int(v_head_dim) if v_head_dim is not None else head_dim
-        self.conv_taps = int(conv_taps) if conv_taps else 1
+        self.has_conv = conv_taps is not None                         # (one tap is a weight per channel and keeps no state)
+        self.conv_taps = int(conv_taps) if self.has_conv else 1
         if self.conv_taps < 1:
-            raise ValueError(f"conv_taps must be >= 1, got {conv_taps}")
+            raise ValueError(f"conv_taps must be >= 1 or None, got {conv_taps}")
         self.softcap = float(softcap) if softcap else None
         if self.softcap is not None and self.softcap <= 0:
             raise ValueError(f"softcap must be positive or None, got {softcap}")
@@ -71,7 +72,7 @@ class PagedAttention(Mixer):
         self.rot_dim = int(getattr(self.position, "dim", 0) or 0)      # rotated values per head (0: none)
         if self.rot_dim > head_dim:
             raise ValueError(f"the position encoding rotates {self.rot_dim} values of a head of {head_dim}")
-        self.general = (self.v_head_dim != head_dim or self.conv_taps > 1 or self.gated or self.qkv_bias
+        self.general = (self.v_head_dim != head_dim or self.has_conv or self.gated or self.qkv_bias
                         or self.rot_dim not in (0, head_dim))
         if self.general and (self.shares_kv or self.bias):
             raise ValueError("the general attention step has neither a shared cache nor an output bias")
@@ -106,7 +107,7 @@ class PagedAttention(Mixer):
             specs[f"{n[key]}{ws}"] = ParamSpec((r, d))
             if self.qkv_bias:
                 specs[f"{n[key]}{self.bias_suffix}"] = ParamSpec((r,), storage="vector", init="normal")
-            if self.conv_taps > 1:
+            if self.has_conv:
                 specs[f"{n[key]}{self.conv_suffix}"] = ParamSpec((r, self.conv_taps), storage="vector", init="normal", std=0.5)
         if self.gated:
             specs[f"{n['g']}{ws}"] = ParamSpec((self.num_heads, d))
@@ -122,7 +123,7 @@ class PagedAttention(Mixer):
             if self.gated:
                 b.append(torch.zeros(self.num_heads, dtype=self.w_in.dtype, device=self.w_in.device))
             self.b_in = torch.cat(b, dim=0).contiguous()
-        if self.conv_taps > 1:                                          # tap-major, 32-bit: a tap's weights lie side by side
+        if self.has_conv:                                               # tap-major, 32-bit: a tap's weights lie side by side
             w = torch.cat([params[f"{n[k]}{self.conv_suffix}"].float() for k in ("q", "k", "v")], dim=0)
             self.conv_w = w.t().contiguous()
 
