@@ -321,7 +321,7 @@ class OpRecorder:
              "scale_add_layernorm", "cast_rows", "latent_store", "latent_query", "gate_heads", "batched_linear", "causal_conv",
              "rglru_scan", "glu", "linear_glu", "grouped_glu", "moe_route", "moe_plan", "grouped_linear", "moe_combine",
              "qkv_conv_rope_store", "conv_tail_update", "gate_head_rows", "token_shift_mix", "wkv_scan", "mlstm_scan", "head_norm_gate",
-             "activation", "linear_act")
+             "activation", "linear_act", "wkv_decay", "mlstm_gates")
 
     def __init__(self, ops):
         self.ops, self.calls, self.orig, self.depth = ops, [], {}, 0
@@ -369,10 +369,10 @@ def op_cost(name, args, kw, out, kv_lens, window):
         # the step's rows in and out, each request's state row read and written once; the recurrence's arithmetic is 32-bit on
         # the ordinary cores: three (wkv) or four (mlstm) multiply-adds per state element and token, returned as a second count
         if name == "wkv_scan":
-            r, state, n, H, D = args[0], args[6], args[11], args[12], args[13]
+            r, state, n, H, D = args[0], args[5], args[10], args[11], args[12]
             T, per_tok, fma = r.shape[0], 3 * H * D * r.element_size() + 8 * H * D, 3 * H * D * D
         else:
-            q, state, n, H, D, Dv = args[0], args[4], args[9], args[10], args[11], args[12]
+            q, state, n, H, D, Dv = args[0], args[4], args[8], args[9], args[10], args[11]
             T, per_tok, fma = q.shape[0], (2 * H * D + H * Dv) * q.element_size() + 4 * H * Dv + 8 * H, 4 * H * D * Dv
         row = state[0].numel() * 4
         return T * per_tok + 2 * n * row, ("fp32", 2 * T * fma)
@@ -381,6 +381,8 @@ def op_cost(name, args, kw, out, kv_lens, window):
     if name == "conv_tail_update":                                 # (proj, channels, taps, tail, qsl, slots, requests)
         return 2 * args[6] * (args[2] - 1) * args[1] * 4, 0
     if name == "token_shift_mix":
+        return _tensor_bytes([args[0], out]), 0
+    if name in ("wkv_decay", "mlstm_gates"):
         return _tensor_bytes([args[0], out]), 0
     if name in ("head_norm_gate", "gate_head_rows"):
         return _tensor_bytes([args[0], args[1], out]), 0

@@ -2,7 +2,7 @@
 // causal convolution, whose rotation covers only the first `rot` values of a head, and whose value size differs from the
 // key size; and the per-head output gate behind the attention kernels.
 //
-//   qkv_conv_rope_store   one CTA per token.  The token's row [q | k | v] (Hq*D + Hkv*D + Hkv*Dv channels) is convolved over
+//   qkv_conv_rope_store   one CTA per token and head.  The token's row [q | k | v] (Hq*D + Hkv*D + Hkv*Dv channels) is convolved over
 //                         time, y_t[c] = sum_k w[k][c] * u_(t - taps + 1 + k)[c] in 32-bit (weights tap-major; inputs before
 //                         the step's first token come from the request's state row, which holds the last taps - 1 projected
 //                         rows, oldest first, and is zero for a new request), q and k are rotated at the token's position
@@ -41,53 +41,59 @@ __device__ __forceinline__ float rotated(const float* x, int i, int rot, int sty
     return (i & 1) ? x[i] * c.x + x[i - 1] * c.y : x[i] * c.x - x[i + 1] * c.y;
 }
 
+// one CTA per (token, head of q, k or v): the head's channels are convolved into shared memory, then rotated and written
 template <typename T>
-__global__ void __launch_bounds__(256) qkv_conv_rope_store_kernel(const QkvArgs a) {
+__global__ void __launch_bounds__(128) qkv_conv_rope_store_kernel(const QkvArgs a) {
     TTIE_PDL_ENTRY();
-    extern __shared__ float row[];                                  // the token's convolved [q | k | v]
-    const int t = blockIdx.x;
+    extern __shared__ float row[];                                  // the head's convolved channels
+    const int t = blockIdx.x, unit = blockIdx.y;
     const int C = a.Hq * a.D + a.Hkv * a.D + a.Hkv * a.Dv;
+    const int kind = unit < a.Hq ? 0 : unit < a.Hq + a.Hkv ? 1 : 2; // q, k, v
+    const int h = kind == 0 ? unit : kind == 1 ? unit - a.Hq : unit - a.Hq - a.Hkv;
+    const int width = kind == 2 ? a.Dv : a.D;
+    const int c0 = kind == 0 ? h * a.D : kind == 1 ? a.Hq * a.D + h * a.D : (a.Hq + a.Hkv) * a.D + h * a.Dv;
+    if (kind != 0 && !a.write_kv) return;
     const T* proj = reinterpret_cast<const T*>(a.proj);
     const int s = a.token_seq[t];
     const int j = t - a.qsl[s];                                     // index among the request's tokens of this step
     if (a.taps > 1) {
         const float* tail = a.tail + (size_t)slot_row_(a.slot_ids[s], a.tail_rows) * (a.taps - 1) * C;
-        for (int c = threadIdx.x; c < C; c += blockDim.x) {
+        for (int i = threadIdx.x; i < width; i += blockDim.x) {
+            const int c = c0 + i;
             float acc = 0.f;
             for (int k = 0; k < a.taps; ++k) {
                 const int src = j - (a.taps - 1) + k;
                 const float u = src >= 0 ? to_f32(proj[(size_t)(t - j + src) * a.ld + c]) : tail[(size_t)(a.taps - 1 + src) * C + c];
                 acc = fmaf(a.conv_w[(size_t)k * C + c], u, acc);
             }
-            row[c] = acc;
+            row[i] = acc;
         }
     } else {
-        for (int c = threadIdx.x; c < C; c += blockDim.x) {
-            const float u = to_f32(proj[(size_t)t * a.ld + c]);
-            row[c] = a.conv_w ? a.conv_w[c] * u : u;
+        for (int i = threadIdx.x; i < width; i += blockDim.x) {
+            const float u = to_f32(proj[(size_t)t * a.ld + c0 + i]);
+            row[i] = a.conv_w ? a.conv_w[c0 + i] * u : u;
         }
     }
     __syncthreads();
     const float2* cs = a.rot > 0 ? a.cs + (size_t)t * (a.rot >> 1) : nullptr;
-    T* q = reinterpret_cast<T*>(a.q_out) + (size_t)t * a.Hq * a.Dp;
-    for (int e = threadIdx.x; e < a.Hq * a.Dp; e += blockDim.x) {
-        const int h = e / a.Dp, i = e - h * a.Dp;
-        q[e] = from_f32<T>(i < a.D ? rotated(row + h * a.D, i, a.rot, a.style, cs) : 0.f);
+    if (kind == 0) {
+        T* q = reinterpret_cast<T*>(a.q_out) + ((size_t)t * a.Hq + h) * a.Dp;
+        for (int i = threadIdx.x; i < a.Dp; i += blockDim.x)
+            q[i] = from_f32<T>(i < a.D ? rotated(row, i, a.rot, a.style, cs) : 0.f);
+        return;
     }
-    if (!a.write_kv) return;
     const int pos = a.positions[t];
     int page = a.block_table[(size_t)s * a.table_width + pos / a.page_size];
     if (page < 0 || page >= a.num_pages) page = 0;                  // validated on the host; never write outside
-    const int off = pos % a.page_size;
-    T* kp = reinterpret_cast<T*>(a.k_pages);
-    T* vp = reinterpret_cast<T*>(a.v_pages);
-    const float* krow = row + a.Hq * a.D;
-    const float* vrow = krow + a.Hkv * a.D;
-    for (int e = threadIdx.x; e < a.Hkv * a.Dp; e += blockDim.x) {
-        const int h = e / a.Dp, i = e - h * a.Dp;
-        const size_t dst = (((size_t)page * a.Hkv + h) * a.page_size + off) * a.Dp + i;
-        kp[dst] = from_f32<T>(i < a.D ? rotated(krow + h * a.D, i, a.rot, a.style, cs) : 0.f);
-        vp[dst] = from_f32<T>(i < a.Dv ? vrow[h * a.Dv + i] : 0.f);
+    const size_t dst = (((size_t)page * a.Hkv + h) * a.page_size + pos % a.page_size) * a.Dp;
+    if (kind == 1) {
+        T* kp = reinterpret_cast<T*>(a.k_pages) + dst;
+        for (int i = threadIdx.x; i < a.Dp; i += blockDim.x)
+            kp[i] = from_f32<T>(i < a.D ? rotated(row, i, a.rot, a.style, cs) : 0.f);
+    } else {
+        T* vp = reinterpret_cast<T*>(a.v_pages) + dst;
+        for (int i = threadIdx.x; i < a.Dp; i += blockDim.x)
+            vp[i] = from_f32<T>(i < a.Dv ? row[i] : 0.f);
     }
 }
 
@@ -120,6 +126,25 @@ __global__ void gate_head_rows_kernel(const T* __restrict__ attn, const T* __res
     }
 }
 
+// bfloat16, eight values per thread (value size and padded size multiples of 8, 16-byte aligned rows)
+__global__ void gate_head_rows_vec8_kernel(const __nv_bfloat16* __restrict__ attn, const __nv_bfloat16* __restrict__ gate, long long ld_gate,
+                                           int T_, int H, int Dv, int Dp, __nv_bfloat16* __restrict__ out) {
+    TTIE_PDL_ENTRY();
+    const int col = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+    if (col >= H * Dv) return;
+    const int h = col / Dv, j = col - h * Dv;
+    for (size_t t = blockIdx.y; t < (size_t)T_; t += gridDim.y) {
+        const uint4 x = *reinterpret_cast<const uint4*>(attn + (t * H + h) * Dp + j);
+        const float g = gate ? 1.0f / (1.0f + expf(-__bfloat162float(gate[t * ld_gate + h]))) : 1.0f;
+        uint4 y;
+        const __nv_bfloat162* a = reinterpret_cast<const __nv_bfloat162*>(&x);
+        __nv_bfloat162* b = reinterpret_cast<__nv_bfloat162*>(&y);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(a[i]); b[i] = __floats2bfloat162_rn(f.x * g, f.y * g); }
+        *reinterpret_cast<uint4*>(out + t * H * Dv + col) = y;
+    }
+}
+
 }  // namespace
 
 extern "C" int ttie_qkv_conv_rope_store(const void* proj, long long ld, int T, int Hq, int Hkv, int D, int Dv, int Dp, int taps,
@@ -137,16 +162,13 @@ extern "C" int ttie_qkv_conv_rope_store(const void* proj, long long ld, int T, i
     a.tail_rows = tail_rows; a.positions = positions; a.token_seq = token_seq; a.qsl = qsl; a.slot_ids = slot_ids;
     a.cs = (const float2*)cs; a.rot = rot; a.style = style; a.q_out = q_out; a.k_pages = k_pages; a.v_pages = v_pages;
     a.block_table = block_table; a.table_width = table_width; a.page_size = page_size; a.num_pages = num_pages; a.write_kv = write_kv;
-    const size_t smem = (size_t)(Hq * D + Hkv * D + Hkv * Dv) * sizeof(float);
-    if (smem > 200 * 1024) TTIE_FAIL("qkv_conv_rope_store: a row of %zu bytes exceeds shared memory", smem);
+    const size_t smem = (size_t)(D > Dv ? D : Dv) * sizeof(float);
+    if (T > 2147483647 / 1 || Hq + 2 * Hkv > 65535) TTIE_FAIL("qkv_conv_rope_store: %d heads exceed the grid", Hq + 2 * Hkv);
     cudaStream_t s = (cudaStream_t)stream;
-    if (dtype == kF32) {
-        if (smem > 48 * 1024) cudaFuncSetAttribute(qkv_conv_rope_store_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        TTIE_LAUNCH(qkv_conv_rope_store_kernel<float>, T, 256, smem, s, a);
-    } else if (dtype == kBF16) {
-        if (smem > 48 * 1024) cudaFuncSetAttribute(qkv_conv_rope_store_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        TTIE_LAUNCH(qkv_conv_rope_store_kernel<__nv_bfloat16>, T, 256, smem, s, a);
-    } else TTIE_FAIL("qkv_conv_rope_store: unknown dtype %d", dtype);
+    dim3 grid(T, Hq + 2 * Hkv);
+    if (dtype == kF32) TTIE_LAUNCH(qkv_conv_rope_store_kernel<float>, grid, 128, smem, s, a);
+    else if (dtype == kBF16) TTIE_LAUNCH(qkv_conv_rope_store_kernel<__nv_bfloat16>, grid, 128, smem, s, a);
+    else TTIE_FAIL("qkv_conv_rope_store: unknown dtype %d", dtype);
     TTIE_CHECK_LAUNCH("qkv_conv_rope_store");
     return 0;
 }
@@ -168,6 +190,13 @@ extern "C" int ttie_gate_head_rows(const void* attn, const void* gate, long long
     if (T <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
     dim3 grid(ceil_div(H * Dv, 256), T < 65535 ? T : 65535);
+    if (dtype == kBF16 && Dv % 8 == 0 && Dp % 8 == 0 && !(((uintptr_t)attn | (uintptr_t)out) & 15)) {
+        dim3 g8(ceil_div(H * Dv / 8, 128), T < 65535 ? T : 65535);
+        TTIE_LAUNCH(gate_head_rows_vec8_kernel, g8, 128, 0, s, (const __nv_bfloat16*)attn, (const __nv_bfloat16*)gate, ld_gate, T, H, Dv, Dp,
+                    (__nv_bfloat16*)out);
+        TTIE_CHECK_LAUNCH("gate_head_rows");
+        return 0;
+    }
     if (dtype == kF32) TTIE_LAUNCH(gate_head_rows_kernel<float>, grid, 256, 0, s, (const float*)attn, (const float*)gate, ld_gate, T, H, Dv, Dp, (float*)out);
     else if (dtype == kBF16) TTIE_LAUNCH(gate_head_rows_kernel<__nv_bfloat16>, grid, 256, 0, s, (const __nv_bfloat16*)attn, (const __nv_bfloat16*)gate, ld_gate, T, H, Dv, Dp, (__nv_bfloat16*)out);
     else TTIE_FAIL("gate_head_rows: unknown dtype %d", dtype);

@@ -3,17 +3,23 @@
 // maximum (mlstm).  All of a recurrence is 32-bit: decays, gates, exponentials, the state and the read-out.
 //
 // Both scans share one layout.  A value column of S moves independently of the others, so a thread owns KPT consecutive key
-// channels of one column: a CTA is (columns x slices) threads for one (request, head), slices = key channels / KPT rounded up
-// to a power of two, the lanes of a column's slices adjacent so that the read-out sum over key channels is a few shuffles.
+// channels of one column (KPT = 4 for heads of up to 128 key channels, 8 up to 256, 16 up to 512: the fewest whose slices fit
+// a warp, because the recurrence offers no other parallelism than its state's elements): a CTA is (columns x slices) threads
+// for one (request, head), slices = key channels / KPT rounded up to a power of two, the lanes of a column's slices adjacent
+// so that the read-out sum over key channels is a few shuffles.
 // The state rows hold S as [head][value column][padded key channels] (a thread's channels are contiguous).  The step's tokens
-// of a request are walked in order, TB at a time staged through shared memory (decays and gates are evaluated while staging);
-// a request may be cut into steps anywhere because the walk starts from the state row and ends by writing it back.
+// of a request are walked in order, a run of tokens at a time staged through shared memory in two stages: the next run's rows
+// travel as asynchronous copies while this run is computed; decays and gates are evaluated before the walk, in parallel over
+// the tokens.
+// A request may be cut into steps anywhere because the walk starts from the state row and ends by writing it back.
 //
 //   token_shift_mix   mixes[m][t] = h_t + (h_(t-1) - h_t) * mu[m]; the previous token of a step's first token is the state row
-//   wkv_scan          o_t = (S + diag(u) k_t v_t^T)^T r_t, then S <- diag(w_t) S + k_t v_t^T, w = exp(-exp(wlog + w0));
+//   wkv_decay         w = exp(-exp(wlog + w0)) per token and key channel
+//   wkv_scan          o_t = (S + diag(u) k_t v_t^T)^T r_t, then S <- diag(w_t) S + k_t v_t^T;
 //                     also stores the request's last mixer input as the next step's previous token
-//   mlstm_scan        i = cap tanh(i'/cap), f = logsigmoid(cap tanh(f'/cap)), m' = max(f + m, i), S <- e^(f+m-m') S + e^(i-m') k v^T,
-//                     n likewise with k alone, o = S^T q / (max(|n.q|, e^(-m')) + 1e-6)
+//   mlstm_gates       i = cap tanh(i'/cap), f = logsigmoid(cap tanh(f'/cap)), m' = max(f + m, i) as prefix operations of a warp;
+//                     per token e^(f+m-m'), e^(i-m'), e^(-m')
+//   mlstm_scan        S <- e^(f+m-m') S + e^(i-m') k v^T, n likewise with k alone, o = S^T q / (max(|n.q|, e^(-m')) + 1e-6)
 //   head_norm_gate    out = o / rms(o over the head) * weight * act(gate)   (act: silu or sigmoid)
 #include "common.cuh"
 #include <math.h>
@@ -21,8 +27,6 @@ using namespace ttie;
 
 namespace {
 
-constexpr int KPT = 16;          // key channels per thread
-constexpr int TB = 16;           // tokens staged at a time
 
 __device__ __forceinline__ int slot_row_(int slot, int num_rows) { return slot < 0 ? num_rows - 1 : slot; }
 
@@ -47,33 +51,114 @@ __global__ void token_shift_mix_kernel(const T* __restrict__ x, long long ld, in
     }
 }
 
+// bfloat16, eight channels per thread (width and row stride multiples of 8, 16-byte aligned arrays)
+__global__ void token_shift_mix_vec8_kernel(const __nv_bfloat16* __restrict__ x, long long ld, int T_, int d, int M, const float* __restrict__ mu,
+                                            const float* __restrict__ prev, int prev_rows, const int* __restrict__ token_seq,
+                                            const int* __restrict__ qsl, const int* __restrict__ slot_ids, __nv_bfloat16* __restrict__ out) {
+    TTIE_PDL_ENTRY();
+    const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+    if (c >= d) return;
+    for (int t = blockIdx.y; t < T_; t += gridDim.y) {
+        const int s = token_seq[t];
+        float h[8], hp[8];
+        const uint4 xv = *reinterpret_cast<const uint4*>(x + (size_t)t * ld + c);
+        const __nv_bfloat162* a = reinterpret_cast<const __nv_bfloat162*>(&xv);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(a[i]); h[2 * i] = f.x; h[2 * i + 1] = f.y; }
+        if (t > qsl[s]) {
+            const uint4 pv = *reinterpret_cast<const uint4*>(x + (size_t)(t - 1) * ld + c);
+            const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&pv);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(b[i]); hp[2 * i] = f.x; hp[2 * i + 1] = f.y; }
+        } else {
+            const float* p = prev + (size_t)slot_row_(slot_ids[s], prev_rows) * d + c;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) hp[i] = p[i];
+        }
+        for (int m = 0; m < M; ++m) {
+            const float4 m0 = *reinterpret_cast<const float4*>(mu + (size_t)m * d + c), m1 = *reinterpret_cast<const float4*>(mu + (size_t)m * d + c + 4);
+            const float w[8] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y, m1.z, m1.w};
+            uint4 y;
+            __nv_bfloat162* o = reinterpret_cast<__nv_bfloat162*>(&y);
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                o[i] = __floats2bfloat162_rn(fmaf(hp[2 * i] - h[2 * i], w[2 * i], h[2 * i]), fmaf(hp[2 * i + 1] - h[2 * i + 1], w[2 * i + 1], h[2 * i + 1]));
+            *reinterpret_cast<uint4*>(out + ((size_t)m * T_ + t) * d + c) = y;
+        }
+    }
+}
+
+// decay of the time mix per token and key channel, once per step: w = exp(-exp(wlog + w0)), 32-bit
+__global__ void wkv_decay_kernel(const float* __restrict__ wlog, long long ld, const float* __restrict__ w0, float* __restrict__ out,
+                                 int T_, int HD) {
+    TTIE_PDL_ENTRY();
+    const long long total = (long long)T_ * HD;
+    for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (long long)gridDim.x * blockDim.x) {
+        const long long t = e / HD;
+        const int c = (int)(e - t * HD);
+        out[e] = expf(-expf(wlog[t * ld + c] + w0[c]));
+    }
+}
+
 struct WkvArgs {
     const void* r; const void* k; const void* v; long long ld;       // [T, H*D] each, compute dtype
-    const float* wlog; long long ld_w; const float* w0; const float* u;
+    const float* decay;                                               // [T, H*D] float32
+    const float* u;
     float* state; int state_rows;                                     // [rows, H, D, Dpad]
     const void* x; long long ld_x; int d; float* prev; int prev_rows; // the mixer's input and the rows that keep its last token
     const int* qsl; const int* slot_ids;
     float* out;                                                       // [T, H*D] float32
-    int H, D, Dpad, slices;
+    int H, D, Dpad, slices, tb; bool vec;                             // tb: tokens per stage; vec: rows can travel as 16-byte copies
 };
 
-template <typename T>
+// ---- staging of a run of tokens into shared memory
+// Rows of D values per token and head go from global to shared memory as 16-byte asynchronous copies (no register in between,
+// so a thread has all of a stage's copies in flight at once and the next stage travels while this one is computed); where the
+// sizes or addresses do not allow that (`vec` false) the same rows are copied value by value.
+__device__ __forceinline__ void cp_async16(void* dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"((unsigned)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" :: "n"(N) : "memory"); }
+
+template <typename E>
+__device__ __forceinline__ void stage_rows(E* dst, int dst_ld, const E* src, long long src_ld, int rows, int D, bool vec) {
+    if (vec) {
+        constexpr int CE = 16 / sizeof(E);
+        const int per_row = D / CE;
+        for (int e = threadIdx.x; e < rows * per_row; e += blockDim.x) {
+            const int tt = e / per_row, j = e - tt * per_row;
+            cp_async16(dst + tt * dst_ld + j * CE, src + (size_t)tt * src_ld + j * CE);
+        }
+    } else {
+        for (int e = threadIdx.x; e < rows * D; e += blockDim.x) {
+            const int tt = e / D, j = e - tt * D;
+            dst[tt * dst_ld + j] = src[(size_t)tt * src_ld + j];
+        }
+    }
+}
+
+constexpr int MAXV = 16;            // staged tokens at most; also the most values of v (or gate weights) a thread carries ahead
+
+template <typename T, int KPT>
 __global__ void __launch_bounds__(128) wkv_scan_kernel(const WkvArgs a) {
     TTIE_PDL_ENTRY();
-    extern __shared__ float sm[];
-    const int cols = blockDim.x / a.slices;
-    float* r_s = sm;                                                 // [TB][Dpad]
-    float* k_s = r_s + TB * a.Dpad;
-    float* w_s = k_s + TB * a.Dpad;
-    float* v_s = w_s + TB * a.Dpad;                                  // [TB][cols]
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int cols = blockDim.x / a.slices, TB = a.tb;
+    // two stages of [r | k] in the compute dtype and w in float32, rows of Dpad values; one array of the columns' v
+    float* w_s = reinterpret_cast<float*>(smem_raw);                                  // [2][TB][Dpad]
+    T* r_s = reinterpret_cast<T*>(w_s + 2 * TB * a.Dpad);                             // [2][TB][Dpad]
+    T* k_s = r_s + 2 * TB * a.Dpad;
+    float* v_s = reinterpret_cast<float*>(k_s + 2 * TB * a.Dpad);                     // [TB][cols]
     const int s = blockIdx.z, h = blockIdx.y;
     const int t0 = a.qsl[s], n = a.qsl[s + 1] - t0;
     const int slice = threadIdx.x % a.slices, cl = threadIdx.x / a.slices;
     const int col = blockIdx.x * cols + cl;
     const bool colv = col < a.D;
     const int HD = a.H * a.D;
+    const int ch0 = slice * KPT;
     const size_t row = slot_row_(a.slot_ids[s], a.state_rows);
-    float* sp = a.state + ((row * a.H + h) * a.D + (colv ? col : 0)) * a.Dpad + slice * KPT;
+    float* sp = a.state + ((row * a.H + h) * a.D + (colv ? col : 0)) * a.Dpad + ch0;
     float S[KPT], ub[KPT];
 #pragma unroll
     for (int i = 0; i < KPT; i += 4) {
@@ -81,44 +166,61 @@ __global__ void __launch_bounds__(128) wkv_scan_kernel(const WkvArgs a) {
         S[i] = x4.x; S[i + 1] = x4.y; S[i + 2] = x4.z; S[i + 3] = x4.w;
     }
 #pragma unroll
-    for (int i = 0; i < KPT; ++i) { const int ch = slice * KPT + i; ub[i] = ch < a.D ? a.u[h * a.D + ch] : 0.f; }
-    const T* rp = reinterpret_cast<const T*>(a.r);
-    const T* kp = reinterpret_cast<const T*>(a.k);
-    const T* vp = reinterpret_cast<const T*>(a.v);
-    for (int c0 = 0; c0 < n; c0 += TB) {
-        const int nb = min(TB, n - c0);
-        __syncthreads();
-        for (int e = threadIdx.x; e < nb * a.Dpad; e += blockDim.x) {
-            const int tt = e / a.Dpad, ch = e - tt * a.Dpad;
-            float rv = 0.f, kv = 0.f, wv = 0.f;
-            if (ch < a.D) {
-                const size_t g = (size_t)(t0 + c0 + tt);
-                rv = to_f32(rp[g * a.ld + h * a.D + ch]);
-                kv = to_f32(kp[g * a.ld + h * a.D + ch]);
-                wv = expf(-expf(a.wlog[g * a.ld_w + h * a.D + ch] + a.w0[h * a.D + ch]));
+    for (int i = 0; i < KPT; ++i) ub[i] = ch0 + i < a.D ? a.u[h * a.D + ch0 + i] : 0.f;
+    const T* rp = reinterpret_cast<const T*>(a.r) + (size_t)t0 * a.ld + h * a.D;
+    const T* kp = reinterpret_cast<const T*>(a.k) + (size_t)t0 * a.ld + h * a.D;
+    const T* vp = reinterpret_cast<const T*>(a.v) + (size_t)t0 * a.ld + h * a.D;
+    const float* wp = a.decay + (size_t)t0 * HD + h * a.D;
+    // channels behind D (a head that does not fill its last slice) read as zero in every stage
+    if (a.Dpad > a.D)
+        for (int e = threadIdx.x; e < 2 * TB * a.Dpad; e += blockDim.x)
+            if (e % a.Dpad >= a.D) { w_s[e] = 0.f; r_s[e] = from_f32<T>(0.f); k_s[e] = from_f32<T>(0.f); }
+    auto stage = [&](int buf, int c0, int nb) {
+        stage_rows<T>(r_s + buf * TB * a.Dpad, a.Dpad, rp + (size_t)c0 * a.ld, a.ld, nb, a.D, a.vec);
+        stage_rows<T>(k_s + buf * TB * a.Dpad, a.Dpad, kp + (size_t)c0 * a.ld, a.ld, nb, a.D, a.vec);
+        stage_rows<float>(w_s + buf * TB * a.Dpad, a.Dpad, wp + (size_t)c0 * HD, HD, nb, a.D, a.vec);
+        cp_async_commit();
+    };
+    float vreg[MAXV];                                                // this thread's share of the next run's v
+    auto fetch_v = [&](int c0, int nb) {
+#pragma unroll
+        for (int i = 0; i < MAXV; ++i) {
+            const int e = i * blockDim.x + threadIdx.x;
+            if (e < nb * cols) {
+                const int tt = e / cols, c = blockIdx.x * cols + (e - tt * cols);
+                vreg[i] = c < a.D ? to_f32(vp[(size_t)(c0 + tt) * a.ld + c]) : 0.f;
             }
-            r_s[e] = rv; k_s[e] = kv; w_s[e] = wv;
         }
-        for (int e = threadIdx.x; e < nb * cols; e += blockDim.x) {
-            const int tt = e / cols, c = blockIdx.x * cols + (e - tt * cols);
-            v_s[e] = c < a.D ? to_f32(vp[(size_t)(t0 + c0 + tt) * a.ld + h * a.D + c]) : 0.f;
+    };
+    stage(0, 0, min(TB, n));
+    fetch_v(0, min(TB, n));
+    for (int c0 = 0, it = 0; c0 < n; c0 += TB, ++it) {
+        const int nb = min(TB, n - c0), buf = it & 1;
+        const bool more = c0 + TB < n;
+        if (more) stage(buf ^ 1, c0 + TB, min(TB, n - c0 - TB));
+#pragma unroll
+        for (int i = 0; i < MAXV; ++i) {
+            const int e = i * blockDim.x + threadIdx.x;
+            if (e < nb * cols) v_s[e] = vreg[i];
         }
+        if (more) { fetch_v(c0 + TB, min(TB, n - c0 - TB)); cp_async_wait<1>(); } else cp_async_wait<0>();
         __syncthreads();
+        const T* rb = r_s + buf * TB * a.Dpad + ch0;
+        const T* kb = k_s + buf * TB * a.Dpad + ch0;
+        const float* wb = w_s + buf * TB * a.Dpad + ch0;
         for (int tt = 0; tt < nb; ++tt) {
             const float vj = v_s[tt * cols + cl];
-            const float* rr = r_s + tt * a.Dpad + slice * KPT;
-            const float* kk = k_s + tt * a.Dpad + slice * KPT;
-            const float* ww = w_s + tt * a.Dpad + slice * KPT;
             float acc = 0.f;
 #pragma unroll
             for (int i = 0; i < KPT; ++i) {
-                const float kv = kk[i] * vj;
-                acc = fmaf(rr[i], fmaf(ub[i], kv, S[i]), acc);
-                S[i] = fmaf(ww[i], S[i], kv);
+                const float kv = to_f32(kb[tt * a.Dpad + i]) * vj;
+                acc = fmaf(to_f32(rb[tt * a.Dpad + i]), fmaf(ub[i], kv, S[i]), acc);
+                S[i] = fmaf(wb[tt * a.Dpad + i], S[i], kv);
             }
             acc = slice_sum(acc, a.slices);
             if (slice == 0 && colv) a.out[(size_t)(t0 + c0 + tt) * HD + h * a.D + col] = acc;
         }
+        __syncthreads();
     }
     if (colv) {
 #pragma unroll
@@ -131,35 +233,74 @@ __global__ void __launch_bounds__(128) wkv_scan_kernel(const WkvArgs a) {
     }
 }
 
-struct MlstmArgs {
-    const void* q; const void* k; const void* v; long long ld;        // q, k [T, H*D]; v [T, H*Dv]; one row stride
-    const float* gates; long long ld_g;                               // [T, 2H]: input gate pre-activations, then forget gate's
-    float* S; float* nrm; float* mx; int state_rows;                  // [rows, H, Dv, Dpad], [rows, H, Dpad], [rows, H]
-    const int* qsl; const int* slot_ids;
-    float* out;                                                       // [T, H*Dv] float32
-    int H, D, Dv, Dpad, slices; float qscale, cap;
-};
-
 __device__ __forceinline__ float logsigmoidf_(float x) { return fminf(x, 0.f) - log1pf(expf(-fabsf(x))); }
 
-template <typename T>
+// The gates of the matrix memory for every token of the step: one warp per (request, head) walks the tokens 32 at a time.
+// With i, f the log gates and F_t the sum of f up to t (from the warp's first token), the running maximum
+// m_t = max(f_t + m_(t-1), i_t) equals F_t + max(m_before, max over s <= t of (i_s - F_s)): a prefix sum and a prefix maximum
+// over the lanes.  Writes per token (state decay e^(f + m_(t-1) - m_t), input weight e^(i - m_t), e^(-m_t)) and moves the
+// request's running maximum in its state row.
+__global__ void __launch_bounds__(32) mlstm_gates_kernel(const float* __restrict__ gates, long long ld_g, float* __restrict__ mx,
+                                                         int state_rows, const int* __restrict__ qsl, const int* __restrict__ slot_ids,
+                                                         float* __restrict__ out, int H, float cap) {
+    TTIE_PDL_ENTRY();
+    const int s = blockIdx.y, h = blockIdx.x, lane = threadIdx.x;
+    const int t0 = qsl[s], n = qsl[s + 1] - t0;
+    float* mrow = mx + (size_t)slot_row_(slot_ids[s], state_rows) * H + h;
+    float m = *mrow;
+    for (int c0 = 0; c0 < n; c0 += 32) {
+        const bool valid = c0 + lane < n;
+        float ig = -INFINITY, fg = 0.f;
+        if (valid) {
+            const float* g = gates + (size_t)(t0 + c0 + lane) * ld_g;
+            ig = cap * tanhf(g[h] / cap);
+            fg = logsigmoidf_(cap * tanhf(g[H + h] / cap));
+        }
+        float F = fg;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) { const float y = __shfl_up_sync(0xffffffffu, F, o); if (lane >= o) F += y; }
+        float X = ig - F;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) { const float y = __shfl_up_sync(0xffffffffu, X, o); if (lane >= o) X = fmaxf(X, y); }
+        const float m_t = F + fmaxf(m, X);
+        float m_prev = __shfl_up_sync(0xffffffffu, m_t, 1);
+        if (lane == 0) m_prev = m;
+        if (valid) {
+            float* o3 = out + ((size_t)(t0 + c0 + lane) * H + h) * 3;
+            o3[0] = expf(fg + m_prev - m_t); o3[1] = expf(ig - m_t); o3[2] = expf(-m_t);
+        }
+        m = __shfl_sync(0xffffffffu, m_t, min(31, n - c0 - 1));
+    }
+    if (lane == 0) *mrow = m;
+}
+
+struct MlstmArgs {
+    const void* q; const void* k; const void* v; long long ld;        // q, k [T, H*D]; v [T, H*Dv]; one row stride
+    const float* gates;                                               // [T, H, 3] from mlstm_gates
+    float* S; float* nrm; int state_rows;                             // [rows, H, Dv, Dpad], [rows, H, Dpad]
+    const int* qsl; const int* slot_ids;
+    float* out;                                                       // [T, H*Dv] float32
+    int H, D, Dv, Dpad, slices, tb; float qscale; bool vec;
+};
+
+template <typename T, int KPT>
 __global__ void __launch_bounds__(128) mlstm_scan_kernel(const MlstmArgs a) {
     TTIE_PDL_ENTRY();
-    extern __shared__ float sm[];
-    const int cols = blockDim.x / a.slices;
-    float* q_s = sm;                                                 // [TB][Dpad]
-    float* k_s = q_s + TB * a.Dpad;
-    float* v_s = k_s + TB * a.Dpad;                                  // [TB][cols]
-    float* g_s = v_s + TB * cols;                                    // [TB][3]: state decay, input weight, e^(-m)
-    __shared__ float m_carry;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int cols = blockDim.x / a.slices, TB = a.tb;
+    T* q_s = reinterpret_cast<T*>(smem_raw);                                          // [2][TB][Dpad]
+    T* k_s = q_s + 2 * TB * a.Dpad;
+    float* v_s = reinterpret_cast<float*>(k_s + 2 * TB * a.Dpad);                     // [TB][cols]
+    float* g_s = v_s + TB * cols;                                                     // [TB][3]: state decay, input weight, e^(-m)
     const int s = blockIdx.z, h = blockIdx.y;
     const int t0 = a.qsl[s], n = a.qsl[s + 1] - t0;
     const int slice = threadIdx.x % a.slices, cl = threadIdx.x / a.slices;
     const int col = blockIdx.x * cols + cl;
     const bool colv = col < a.Dv;
+    const int ch0 = slice * KPT;
     const size_t row = slot_row_(a.slot_ids[s], a.state_rows);
-    float* sp = a.S + ((row * a.H + h) * a.Dv + (colv ? col : 0)) * a.Dpad + slice * KPT;
-    float* np = a.nrm + (row * a.H + h) * a.Dpad + slice * KPT;
+    float* sp = a.S + ((row * a.H + h) * a.Dv + (colv ? col : 0)) * a.Dpad + ch0;
+    float* np = a.nrm + (row * a.H + h) * a.Dpad + ch0;
     float S[KPT], nv[KPT];
 #pragma unroll
     for (int i = 0; i < KPT; i += 4) {
@@ -168,61 +309,73 @@ __global__ void __launch_bounds__(128) mlstm_scan_kernel(const MlstmArgs a) {
         const float4 n4 = *reinterpret_cast<const float4*>(np + i);
         nv[i] = n4.x; nv[i + 1] = n4.y; nv[i + 2] = n4.z; nv[i + 3] = n4.w;
     }
-    if (threadIdx.x == 0) m_carry = a.mx[row * a.H + h];
-    const T* qp = reinterpret_cast<const T*>(a.q);
-    const T* kp = reinterpret_cast<const T*>(a.k);
-    const T* vp = reinterpret_cast<const T*>(a.v);
-    for (int c0 = 0; c0 < n; c0 += TB) {
-        const int nb = min(TB, n - c0);
-        __syncthreads();
-        for (int e = threadIdx.x; e < nb * a.Dpad; e += blockDim.x) {
-            const int tt = e / a.Dpad, ch = e - tt * a.Dpad;
-            float qv = 0.f, kv = 0.f;
-            if (ch < a.D) {
-                const size_t g = (size_t)(t0 + c0 + tt);
-                qv = to_f32(qp[g * a.ld + h * a.D + ch]) * a.qscale;
-                kv = to_f32(kp[g * a.ld + h * a.D + ch]);
+    const T* qp = reinterpret_cast<const T*>(a.q) + (size_t)t0 * a.ld + h * a.D;
+    const T* kp = reinterpret_cast<const T*>(a.k) + (size_t)t0 * a.ld + h * a.D;
+    const T* vp = reinterpret_cast<const T*>(a.v) + (size_t)t0 * a.ld + h * a.Dv;
+    const float* gp = a.gates + ((size_t)t0 * a.H + h) * 3;
+    if (a.Dpad > a.D)
+        for (int e = threadIdx.x; e < 2 * TB * a.Dpad; e += blockDim.x)
+            if (e % a.Dpad >= a.D) { q_s[e] = from_f32<T>(0.f); k_s[e] = from_f32<T>(0.f); }
+    auto stage = [&](int buf, int c0, int nb) {
+        stage_rows<T>(q_s + buf * TB * a.Dpad, a.Dpad, qp + (size_t)c0 * a.ld, a.ld, nb, a.D, a.vec);
+        stage_rows<T>(k_s + buf * TB * a.Dpad, a.Dpad, kp + (size_t)c0 * a.ld, a.ld, nb, a.D, a.vec);
+        cp_async_commit();
+    };
+    float vreg[MAXV], greg[2] = {0.f, 0.f};                          // this thread's share of the next run's v and gate weights
+    auto fetch_v = [&](int c0, int nb) {
+#pragma unroll
+        for (int i = 0; i < MAXV; ++i) {
+            const int e = i * blockDim.x + threadIdx.x;
+            if (e < nb * cols) {
+                const int tt = e / cols, c = blockIdx.x * cols + (e - tt * cols);
+                vreg[i] = c < a.Dv ? to_f32(vp[(size_t)(c0 + tt) * a.ld + c]) : 0.f;
             }
-            q_s[e] = qv; k_s[e] = kv;
         }
-        for (int e = threadIdx.x; e < nb * cols; e += blockDim.x) {
-            const int tt = e / cols, c = blockIdx.x * cols + (e - tt * cols);
-            v_s[e] = c < a.Dv ? to_f32(vp[(size_t)(t0 + c0 + tt) * a.ld + h * a.Dv + c]) : 0.f;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int e = i * blockDim.x + threadIdx.x;
+            if (e < nb * 3) greg[i] = gp[(size_t)(c0 + e / 3) * a.H * 3 + e % 3];
         }
-        if (threadIdx.x == 0) {                                      // the gates' scalar recurrence over the staged tokens
-            float m = m_carry;
-            for (int tt = 0; tt < nb; ++tt) {
-                const float* g = a.gates + (size_t)(t0 + c0 + tt) * a.ld_g;
-                const float ig = a.cap * tanhf(g[h] / a.cap);
-                const float fg = logsigmoidf_(a.cap * tanhf(g[a.H + h] / a.cap));
-                const float m_new = fmaxf(fg + m, ig);
-                g_s[3 * tt] = expf(fg + m - m_new);
-                g_s[3 * tt + 1] = expf(ig - m_new);
-                g_s[3 * tt + 2] = expf(-m_new);
-                m = m_new;
-            }
-            m_carry = m;
+    };
+    stage(0, 0, min(TB, n));
+    fetch_v(0, min(TB, n));
+    for (int c0 = 0, it = 0; c0 < n; c0 += TB, ++it) {
+        const int nb = min(TB, n - c0), buf = it & 1;
+        const bool more = c0 + TB < n;
+        if (more) stage(buf ^ 1, c0 + TB, min(TB, n - c0 - TB));
+#pragma unroll
+        for (int i = 0; i < MAXV; ++i) {
+            const int e = i * blockDim.x + threadIdx.x;
+            if (e < nb * cols) v_s[e] = vreg[i];
         }
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int e = i * blockDim.x + threadIdx.x;
+            if (e < nb * 3) g_s[e] = greg[i];
+        }
+        if (more) { fetch_v(c0 + TB, min(TB, n - c0 - TB)); cp_async_wait<1>(); } else cp_async_wait<0>();
         __syncthreads();
+        const T* qb = q_s + buf * TB * a.Dpad + ch0;
+        const T* kb = k_s + buf * TB * a.Dpad + ch0;
         for (int tt = 0; tt < nb; ++tt) {
             const float vj = v_s[tt * cols + cl];
             const float fa = g_s[3 * tt], ib = g_s[3 * tt + 1];
-            const float* qq = q_s + tt * a.Dpad + slice * KPT;
-            const float* kk = k_s + tt * a.Dpad + slice * KPT;
             float num = 0.f, nq = 0.f;
 #pragma unroll
             for (int i = 0; i < KPT; ++i) {
-                const float bk = ib * kk[i];
+                const float bk = ib * to_f32(kb[tt * a.Dpad + i]);
+                const float qv = to_f32(qb[tt * a.Dpad + i]) * a.qscale;
                 S[i] = fmaf(fa, S[i], bk * vj);
                 nv[i] = fmaf(fa, nv[i], bk);
-                num = fmaf(S[i], qq[i], num);
-                nq = fmaf(nv[i], qq[i], nq);
+                num = fmaf(S[i], qv, num);
+                nq = fmaf(nv[i], qv, nq);
             }
             num = slice_sum(num, a.slices);
             nq = slice_sum(nq, a.slices);
             if (slice == 0 && colv)
                 a.out[(size_t)(t0 + c0 + tt) * a.H * a.Dv + h * a.Dv + col] = num / (fmaxf(fabsf(nq), g_s[3 * tt + 2]) + 1e-6f);
         }
+        __syncthreads();
     }
     if (colv) {
 #pragma unroll
@@ -232,8 +385,6 @@ __global__ void __launch_bounds__(128) mlstm_scan_kernel(const MlstmArgs a) {
 #pragma unroll
         for (int i = 0; i < KPT; i += 4) *reinterpret_cast<float4*>(np + i) = make_float4(nv[i], nv[i + 1], nv[i + 2], nv[i + 3]);
     }
-    __syncthreads();
-    if (blockIdx.x == 0 && threadIdx.x == 0) a.mx[row * a.H + h] = m_carry;
 }
 
 // one warp per (token, head)
@@ -258,15 +409,18 @@ __global__ void head_norm_gate_kernel(const float* __restrict__ o, const T* __re
     }
 }
 
-int scan_shape(int D, int cols_total, int units, int* slices, int* threads) {
+// Key channels per thread for heads of D key channels: the fewest (the most threads per state) whose slices still fit a warp.
+int keys_per_thread(int D) { return D <= 128 ? 4 : D <= 256 ? 8 : 16; }
+
+int scan_shape(int D, int cols_total, int units, int* kpt, int* slices, int* threads) {
+    const int k = keys_per_thread(D);
     int sl = 1;
-    while (sl * KPT < D) sl <<= 1;
+    while (sl * k < D) sl <<= 1;
     if (sl > 32) return -1;
-    *slices = sl;
+    *kpt = k; *slices = sl;
     // few (request, head) units: narrower CTAs so that the columns spread over more SMs
     int th = 128;
     while (th > 32 && (long long)units * ceil_div(cols_total, th / sl) < 2LL * num_sms()) th >>= 1;
-    if (th < sl) th = sl < 32 ? 32 : sl;
     *threads = th;
     return 0;
 }
@@ -274,9 +428,27 @@ int scan_shape(int D, int cols_total, int units, int* slices, int* threads) {
 }  // namespace
 
 extern "C" int ttie_matrix_state_pad(int D) {                        // padded key channels of a state row
+    const int k = keys_per_thread(D);
     int sl = 1;
-    while (sl * KPT < D) sl <<= 1;
-    return sl * KPT;
+    while (sl * k < D) sl <<= 1;
+    return sl * k;
+}
+
+extern "C" int ttie_wkv_decay(const float* wlog, long long ld, const float* w0, float* out, int T, int HD, void* stream) {
+    if (T <= 0) return 0;
+    const long long total = (long long)T * HD;
+    const int grid = (int)((total + 255) / 256 < 148LL * 16 ? (total + 255) / 256 : 148LL * 16);
+    TTIE_LAUNCH(wkv_decay_kernel, grid, 256, 0, (cudaStream_t)stream, wlog, ld, w0, out, T, HD);
+    TTIE_CHECK_LAUNCH("wkv_decay");
+    return 0;
+}
+
+extern "C" int ttie_mlstm_gates(const float* gates, long long ld_g, float* mx, int state_rows, const int* qsl, const int* slot_ids,
+                                int num_seqs, float* out, int H, float cap, void* stream) {
+    if (num_seqs <= 0) return 0;
+    TTIE_LAUNCH(mlstm_gates_kernel, dim3(H, num_seqs), 32, 0, (cudaStream_t)stream, gates, ld_g, mx, state_rows, qsl, slot_ids, out, H, cap);
+    TTIE_CHECK_LAUNCH("mlstm_gates");
+    return 0;
 }
 
 extern "C" int ttie_token_shift_mix(const void* x, long long ld, int T, int d, int M, const float* mu, const float* prev, int prev_rows,
@@ -284,6 +456,13 @@ extern "C" int ttie_token_shift_mix(const void* x, long long ld, int T, int d, i
     if (T <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
     dim3 grid(ceil_div(d, 256), T < 65535 ? T : 65535);
+    if (dtype == kBF16 && d % 8 == 0 && ld % 8 == 0 && !(((uintptr_t)x | (uintptr_t)out | (uintptr_t)mu) & 15)) {
+        dim3 g8(ceil_div(d / 8, 128), T < 65535 ? T : 65535);
+        TTIE_LAUNCH(token_shift_mix_vec8_kernel, g8, 128, 0, s, (const __nv_bfloat16*)x, ld, T, d, M, mu, prev, prev_rows, token_seq, qsl, slot_ids,
+                    (__nv_bfloat16*)out);
+        TTIE_CHECK_LAUNCH("token_shift_mix");
+        return 0;
+    }
     if (dtype == kF32) TTIE_LAUNCH(token_shift_mix_kernel<float>, grid, 256, 0, s, (const float*)x, ld, T, d, M, mu, prev, prev_rows, token_seq, qsl, slot_ids, (float*)out);
     else if (dtype == kBF16) TTIE_LAUNCH(token_shift_mix_kernel<__nv_bfloat16>, grid, 256, 0, s, (const __nv_bfloat16*)x, ld, T, d, M, mu, prev, prev_rows, token_seq, qsl, slot_ids, (__nv_bfloat16*)out);
     else TTIE_FAIL("token_shift_mix: unknown dtype %d", dtype);
@@ -291,54 +470,66 @@ extern "C" int ttie_token_shift_mix(const void* x, long long ld, int T, int d, i
     return 0;
 }
 
-extern "C" int ttie_wkv_scan(const void* r, const void* k, const void* v, long long ld, const float* wlog, long long ld_w, const float* w0,
-                             const float* u, float* state, int state_rows, const void* x, long long ld_x, int d, float* prev,
-                             int prev_rows, const int* qsl, const int* slot_ids, int num_seqs, float* out, int H, int D, int dtype,
-                             void* stream) {
+template <typename T, int KPT, typename Args>
+int launch_scan(void (*kernel)(const Args), const Args& a, dim3 grid, int threads, size_t smem, cudaStream_t s) {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);   // (wide heads)
+    return TTIE_LAUNCH(kernel, grid, threads, smem, s, a) == cudaSuccess ? 0 : -1;
+}
+
+#define TTIE_SCAN_DISPATCH(KERNEL, ARGS)                                                                            \
+    do {                                                                                                            \
+        if (dtype != kF32 && dtype != kBF16) TTIE_FAIL(#KERNEL ": unknown dtype %d", dtype);                         \
+        if (kpt == 4) { if (dtype == kF32) launch_scan<float, 4, ARGS>(KERNEL<float, 4>, a, grid, threads, smem, s); \
+                        else launch_scan<__nv_bfloat16, 4, ARGS>(KERNEL<__nv_bfloat16, 4>, a, grid, threads, smem, s); } \
+        else if (kpt == 8) { if (dtype == kF32) launch_scan<float, 8, ARGS>(KERNEL<float, 8>, a, grid, threads, smem, s); \
+                             else launch_scan<__nv_bfloat16, 8, ARGS>(KERNEL<__nv_bfloat16, 8>, a, grid, threads, smem, s); } \
+        else { if (dtype == kF32) launch_scan<float, 16, ARGS>(KERNEL<float, 16>, a, grid, threads, smem, s);        \
+               else launch_scan<__nv_bfloat16, 16, ARGS>(KERNEL<__nv_bfloat16, 16>, a, grid, threads, smem, s); }   \
+    } while (0)
+
+extern "C" int ttie_wkv_scan(const void* r, const void* k, const void* v, long long ld, const float* decay, const float* u, float* state,
+                             int state_rows, const void* x, long long ld_x, int d, float* prev, int prev_rows, const int* qsl,
+                             const int* slot_ids, int num_seqs, float* out, int H, int D, int dtype, void* stream) {
     if (num_seqs <= 0) return 0;
     WkvArgs a;
-    a.r = r; a.k = k; a.v = v; a.ld = ld; a.wlog = wlog; a.ld_w = ld_w; a.w0 = w0; a.u = u; a.state = state; a.state_rows = state_rows;
+    a.r = r; a.k = k; a.v = v; a.ld = ld; a.decay = decay; a.u = u; a.state = state; a.state_rows = state_rows;
     a.x = x; a.ld_x = ld_x; a.d = d; a.prev = prev; a.prev_rows = prev_rows; a.qsl = qsl; a.slot_ids = slot_ids; a.out = out;
     a.H = H; a.D = D;
-    int threads;
-    if (scan_shape(D, D, num_seqs * H, &a.slices, &threads)) TTIE_FAIL("wkv_scan: %d key channels per head (at most %d)", D, 32 * KPT);
-    a.Dpad = a.slices * KPT;
+    int threads, kpt;
+    if (scan_shape(D, D, num_seqs * H, &kpt, &a.slices, &threads)) TTIE_FAIL("wkv_scan: %d key channels per head (at most 512)", D);
+    a.Dpad = a.slices * kpt;
     const int cols = threads / a.slices;
-    const size_t smem = (size_t)TB * (3 * a.Dpad + cols) * sizeof(float);
+    const int es = dtype == kF32 ? 4 : 2, ce = 16 / es;                // bytes per value of r and k; values per 16-byte copy
+    a.tb = a.Dpad <= 128 ? 16 : a.Dpad <= 256 ? 8 : 4;
+    if (threads * MAXV < a.tb * cols) TTIE_FAIL("wkv_scan: internal: %d threads cannot carry %d x %d values", threads, a.tb, cols);
+    const size_t smem = (size_t)2 * a.tb * a.Dpad * (4 + 2 * es) + (size_t)a.tb * cols * 4;
+    a.vec = D % ce == 0 && D % 4 == 0 && ld % ce == 0 && !(((uintptr_t)r | (uintptr_t)k | (uintptr_t)decay) & 15);
     dim3 grid(ceil_div(D, cols), H, num_seqs);
     cudaStream_t s = (cudaStream_t)stream;
-    if (smem > 48 * 1024) {                                          // (wide heads: more staging than a kernel gets unasked)
-        cudaFuncSetAttribute(wkv_scan_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        cudaFuncSetAttribute(wkv_scan_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    }
-    if (dtype == kF32) TTIE_LAUNCH(wkv_scan_kernel<float>, grid, threads, smem, s, a);
-    else if (dtype == kBF16) TTIE_LAUNCH(wkv_scan_kernel<__nv_bfloat16>, grid, threads, smem, s, a);
-    else TTIE_FAIL("wkv_scan: unknown dtype %d", dtype);
+    TTIE_SCAN_DISPATCH(wkv_scan_kernel, WkvArgs);
     TTIE_CHECK_LAUNCH("wkv_scan");
     return 0;
 }
 
-extern "C" int ttie_mlstm_scan(const void* q, const void* k, const void* v, long long ld, const float* gates, long long ld_g, float* S,
-                               float* nrm, float* mx, int state_rows, const int* qsl, const int* slot_ids, int num_seqs, float* out,
-                               int H, int D, int Dv, float qscale, float cap, int dtype, void* stream) {
+extern "C" int ttie_mlstm_scan(const void* q, const void* k, const void* v, long long ld, const float* gates, float* S, float* nrm,
+                               int state_rows, const int* qsl, const int* slot_ids, int num_seqs, float* out, int H, int D, int Dv,
+                               float qscale, int dtype, void* stream) {
     if (num_seqs <= 0) return 0;
     MlstmArgs a;
-    a.q = q; a.k = k; a.v = v; a.ld = ld; a.gates = gates; a.ld_g = ld_g; a.S = S; a.nrm = nrm; a.mx = mx; a.state_rows = state_rows;
-    a.qsl = qsl; a.slot_ids = slot_ids; a.out = out; a.H = H; a.D = D; a.Dv = Dv; a.qscale = qscale; a.cap = cap;
-    int threads;
-    if (scan_shape(D, Dv, num_seqs * H, &a.slices, &threads)) TTIE_FAIL("mlstm_scan: %d key channels per head (at most %d)", D, 32 * KPT);
-    a.Dpad = a.slices * KPT;
+    a.q = q; a.k = k; a.v = v; a.ld = ld; a.gates = gates; a.S = S; a.nrm = nrm; a.state_rows = state_rows;
+    a.qsl = qsl; a.slot_ids = slot_ids; a.out = out; a.H = H; a.D = D; a.Dv = Dv; a.qscale = qscale;
+    int threads, kpt;
+    if (scan_shape(D, Dv, num_seqs * H, &kpt, &a.slices, &threads)) TTIE_FAIL("mlstm_scan: %d key channels per head (at most 512)", D);
+    a.Dpad = a.slices * kpt;
     const int cols = threads / a.slices;
-    const size_t smem = (size_t)TB * (2 * a.Dpad + cols + 3) * sizeof(float);
+    const int es = dtype == kF32 ? 4 : 2, ce = 16 / es;
+    a.tb = a.Dpad <= 128 ? 16 : a.Dpad <= 256 ? 8 : 4;
+    if (threads * MAXV < a.tb * cols || 2 * threads < a.tb * 3) TTIE_FAIL("mlstm_scan: internal: %d threads cannot carry %d x %d values", threads, a.tb, cols);
+    const size_t smem = (size_t)2 * a.tb * a.Dpad * 2 * es + (size_t)a.tb * (cols + 3) * 4;
+    a.vec = D % ce == 0 && ld % ce == 0 && !(((uintptr_t)q | (uintptr_t)k) & 15);
     dim3 grid(ceil_div(Dv, cols), H, num_seqs);
     cudaStream_t s = (cudaStream_t)stream;
-    if (smem > 48 * 1024) {
-        cudaFuncSetAttribute(mlstm_scan_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        cudaFuncSetAttribute(mlstm_scan_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    }
-    if (dtype == kF32) TTIE_LAUNCH(mlstm_scan_kernel<float>, grid, threads, smem, s, a);
-    else if (dtype == kBF16) TTIE_LAUNCH(mlstm_scan_kernel<__nv_bfloat16>, grid, threads, smem, s, a);
-    else TTIE_FAIL("mlstm_scan: unknown dtype %d", dtype);
+    TTIE_SCAN_DISPATCH(mlstm_scan_kernel, MlstmArgs);
     TTIE_CHECK_LAUNCH("mlstm_scan");
     return 0;
 }

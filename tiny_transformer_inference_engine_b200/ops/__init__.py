@@ -83,10 +83,12 @@ _SIGNATURES = {
     "ttie_gate_head_rows": [_c_void, _c_void, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_void, _c_int, _c_void],
     "ttie_token_shift_mix": [_c_void, _c_ll, _c_int, _c_int, _c_int, _c_void, _c_void, _c_int, _c_void, _c_void, _c_void, _c_void, _c_int,
                              _c_void],
-    "ttie_wkv_scan": [_c_void, _c_void, _c_void, _c_ll, _c_void, _c_ll, _c_void, _c_void, _c_void, _c_int, _c_void, _c_ll, _c_int, _c_void,
+    "ttie_wkv_decay": [_c_void, _c_ll, _c_void, _c_void, _c_int, _c_int, _c_void],
+    "ttie_wkv_scan": [_c_void, _c_void, _c_void, _c_ll, _c_void, _c_void, _c_void, _c_int, _c_void, _c_ll, _c_int, _c_void,
                       _c_int, _c_void, _c_void, _c_int, _c_void, _c_int, _c_int, _c_int, _c_void],
-    "ttie_mlstm_scan": [_c_void, _c_void, _c_void, _c_ll, _c_void, _c_ll, _c_void, _c_void, _c_void, _c_int, _c_void, _c_void, _c_int,
-                        _c_void, _c_int, _c_int, _c_int, _c_float, _c_float, _c_int, _c_void],
+    "ttie_mlstm_gates": [_c_void, _c_ll, _c_void, _c_int, _c_void, _c_void, _c_int, _c_void, _c_int, _c_float, _c_void],
+    "ttie_mlstm_scan": [_c_void, _c_void, _c_void, _c_ll, _c_void, _c_void, _c_void, _c_int, _c_void, _c_void, _c_int,
+                        _c_void, _c_int, _c_int, _c_int, _c_float, _c_int, _c_void],
     "ttie_head_norm_gate": [_c_void, _c_void, _c_ll, _c_void, _c_int, _c_int, _c_int, _c_float, _c_int, _c_void, _c_int, _c_void],
     "ttie_activation": [_c_void, _c_void, _c_ll, _c_int, _c_float, _c_int, _c_int, _c_void],
     "ttie_matrix_state_pad": [_c_int],
@@ -977,15 +979,15 @@ class CudaOps:
         return out
 
     # ---- recurrent layers with a matrix state per head
-    MATRIX_STATE_KEYS_PER_THREAD = 16
-
-    @classmethod
-    def matrix_state_pad(cls, dim: int) -> int:
-        """Key channels of a matrix-state row as the scan kernels lay it out: a power-of-two number of slices of 16."""
+    @staticmethod
+    def matrix_state_pad(dim: int) -> int:
+        """Key channels of a matrix-state row as the scan kernels lay it out: a power-of-two number of slices of 4 (heads of up
+        to 128 key channels), 8 (up to 256) or 16 channels."""
+        per_thread = 4 if dim <= 128 else 8 if dim <= 256 else 16
         slices = 1
-        while slices * cls.MATRIX_STATE_KEYS_PER_THREAD < dim:
+        while slices * per_thread < dim:
             slices *= 2
-        return slices * cls.MATRIX_STATE_KEYS_PER_THREAD
+        return slices * per_thread
 
     def token_shift_mix(self, x, mu, prev, token_seq, query_start_loc, slot_ids):
         """mixes[m, t] = x[t] + (x[t-1] - x[t]) * mu[m]; a request's first token of the step takes x[t-1] from its row of
@@ -999,33 +1001,52 @@ class CudaOps:
         self.launches += 1
         return out
 
-    def wkv_scan(self, r, k, v, wlog, w0, u, state, x, prev, query_start_loc, slot_ids, num_seqs, num_heads, dim):
+    def wkv_decay(self, wlog, w0):
+        """exp(-exp(wlog + w0)) in 32-bit: wlog float32 [T, H*dim] (a row stride allowed), w0 float32 [H*dim] -> [T, H*dim]."""
+        T, HD = wlog.shape
+        out = torch.empty((T, HD), dtype=torch.float32, device=wlog.device)
+        self._check(self.lib.ttie_wkv_decay(_ptr(wlog), wlog.stride(0), _ptr(w0), _ptr(out), T, HD, self._stream(wlog)), "wkv_decay")
+        self.launches += 1
+        return out
+
+    def wkv_scan(self, r, k, v, decay, u, state, x, prev, query_start_loc, slot_ids, num_seqs, num_heads, dim):
         """The time mix's recurrence over the step's tokens from the state rows ``state`` [slots + 1, H, dim, padded dim]
-        (advanced in place): o_t = (S + diag(u) k v^T)^T r, then S <- diag(w) S + k v^T with w = exp(-exp(wlog + w0)).
-        r, k, v [T, H*dim] views with one row stride; wlog float32 [T, H*dim].  Also stores each request's last row of ``x``
-        into ``prev``.  Returns o float32 [T, H*dim]."""
+        (advanced in place): o_t = (S + diag(u) k v^T)^T r, then S <- diag(w) S + k v^T.  r, k, v [T, H*dim] views with one row
+        stride; ``decay`` (w) float32 [T, H*dim] contiguous.  Also stores each request's last row of ``x`` into ``prev``.
+        Returns o float32 [T, H*dim]."""
         T = r.shape[0]
         out = torch.empty((T, num_heads * dim), dtype=torch.float32, device=r.device)
         if not (r.stride(0) == k.stride(0) == v.stride(0)):
             raise KernelError("wkv_scan: r, k and v must share a row stride")
-        self._check(self.lib.ttie_wkv_scan(_ptr(r), _ptr(k), _ptr(v), r.stride(0), _ptr(wlog), wlog.stride(0), _ptr(w0), _ptr(u),
+        self._check(self.lib.ttie_wkv_scan(_ptr(r), _ptr(k), _ptr(v), r.stride(0), _ptr(decay), _ptr(u),
                                            _ptr(state), state.shape[0], _ptr(x), x.stride(0), x.shape[1], _ptr(prev), prev.shape[0],
                                            _ptr(query_start_loc), _ptr(slot_ids), int(num_seqs), _ptr(out), num_heads, dim,
                                            self._dt(r), self._stream(r)), "wkv_scan")
         self.launches += 1
         return out
 
-    def mlstm_scan(self, q, k, v, gates, S, n, m, query_start_loc, slot_ids, num_seqs, num_heads, dim, v_dim, q_scale, cap):
-        """The matrix memory's recurrence over the step's tokens from the state rows S [slots + 1, H, v_dim, padded dim],
-        n [slots + 1, H, padded dim], m [slots + 1, H] (advanced in place).  q, k [T, H*dim], v [T, H*v_dim]: views with one row
-        stride; ``gates`` float32 [T, 2H], input-gate pre-activations then the forget gate's.  Returns o float32 [T, H*v_dim]."""
+    def mlstm_gates(self, pre, m, query_start_loc, slot_ids, num_seqs, num_heads, cap):
+        """Per token and head (state decay, input weight, exp(-running maximum)) from the gate pre-activations ``pre`` float32
+        [T, 2H] (input gate's, then forget gate's), with log gates capped at ``cap``; the running maximum of every request
+        moves in its row of ``m`` [slots + 1, H].  Returns float32 [T, H, 3]."""
+        T = pre.shape[0]
+        out = torch.empty((T, num_heads, 3), dtype=torch.float32, device=pre.device)
+        self._check(self.lib.ttie_mlstm_gates(_ptr(pre), pre.stride(0), _ptr(m), m.shape[0], _ptr(query_start_loc), _ptr(slot_ids),
+                                              int(num_seqs), _ptr(out), num_heads, float(cap), self._stream(pre)), "mlstm_gates")
+        self.launches += 1
+        return out
+
+    def mlstm_scan(self, q, k, v, gates, S, n, query_start_loc, slot_ids, num_seqs, num_heads, dim, v_dim, q_scale):
+        """The matrix memory's recurrence over the step's tokens from the state rows S [slots + 1, H, v_dim, padded dim] and
+        n [slots + 1, H, padded dim] (advanced in place).  q, k [T, H*dim], v [T, H*v_dim]: views with one row stride;
+        ``gates`` from ``mlstm_gates``.  Returns o float32 [T, H*v_dim]."""
         T = q.shape[0]
         out = torch.empty((T, num_heads * v_dim), dtype=torch.float32, device=q.device)
         if not (q.stride(0) == k.stride(0) == v.stride(0)):
             raise KernelError("mlstm_scan: q, k and v must share a row stride")
-        self._check(self.lib.ttie_mlstm_scan(_ptr(q), _ptr(k), _ptr(v), q.stride(0), _ptr(gates), gates.stride(0), _ptr(S), _ptr(n), _ptr(m),
+        self._check(self.lib.ttie_mlstm_scan(_ptr(q), _ptr(k), _ptr(v), q.stride(0), _ptr(gates), _ptr(S), _ptr(n),
                                              S.shape[0], _ptr(query_start_loc), _ptr(slot_ids), int(num_seqs), _ptr(out), num_heads,
-                                             dim, v_dim, float(q_scale), float(cap), self._dt(q), self._stream(q)), "mlstm_scan")
+                                             dim, v_dim, float(q_scale), self._dt(q), self._stream(q)), "mlstm_scan")
         self.launches += 1
         return out
 

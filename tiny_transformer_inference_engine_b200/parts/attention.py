@@ -145,8 +145,6 @@ class PagedAttention(Mixer):
         check = getattr(ops, "check_attention", None)
         if check is not None:
             check(dtype, self.num_heads, self.num_kv_heads, self.padded_dim, self.page_size or page_size)
-        if self.general and self.channels * 4 > 200 * 1024:
-            raise ValueError(f"attention: {self.channels} q/k/v channels exceed what the convolve-rotate-store kernel stages")
 
     # ---------------------------------------------------------------- cache
     def cache_needs(self):

@@ -22,7 +22,7 @@ from typing import Dict, Optional
 import torch
 
 from .base import Mixer, ParamSpec, FixedStateNeed, StepContext
-from .wkv import padded_keys, KEYS_PER_THREAD
+from .wkv import padded_keys, MAX_KEYS
 from ..registry import register_part
 
 DENOMINATOR_FLOOR = 1e-6        # added to the read-out's denominator (the scan kernel carries the same constant)
@@ -35,8 +35,8 @@ class MLSTM(Mixer):
         super().__init__(prefix)
         self.d_model, self.num_heads, self.dim, self.vdim = int(d_model), int(num_heads), int(dim), int(vdim)
         self.gate_cap, self.eps = float(gate_cap), float(eps)
-        if self.dim > 32 * KEYS_PER_THREAD:
-            raise ValueError(f"mlstm: {dim} key channels per head (at most {32 * KEYS_PER_THREAD})")
+        if self.dim > MAX_KEYS:
+            raise ValueError(f"mlstm: {dim} key channels per head (at most {MAX_KEYS})")
         if not self.gate_cap > 0:
             raise ValueError(f"mlstm: gate_cap must be positive, got {gate_cap}")
         self.names = {"q": "q", "k": "k", "v": "v", "g": "g", "i": "i", "i_bias": "i.b", "f": "f", "f_bias": "f.b",
@@ -74,7 +74,8 @@ class MLSTM(Mixer):
         proj = ops.linear(x, self.w_in, None)                                                  # [T, q | k | v | g]
         gates = ops.linear(x, self.w_gates, self.b_gates, out_dtype=torch.float32)             # [T, 2H] float32
         q, k, v, g = proj[:, :H * D], proj[:, H * D:2 * H * D], proj[:, 2 * H * D:2 * H * D + H * Dv], proj[:, 2 * H * D + H * Dv:]
-        o = ops.mlstm_scan(q, k, v, gates, S.state, nrm.state, mx.state, ctx.query_start_loc, ctx.slot_ids, ctx.num_seqs,
-                           H, D, Dv, D ** -0.5, self.gate_cap)
+        weights = ops.mlstm_gates(gates, mx.state, ctx.query_start_loc, ctx.slot_ids, ctx.num_seqs, H, self.gate_cap)
+        o = ops.mlstm_scan(q, k, v, weights, S.state, nrm.state, ctx.query_start_loc, ctx.slot_ids, ctx.num_seqs,
+                           H, D, Dv, D ** -0.5)
         y = ops.head_norm_gate(o, g, self.norm_w, H, Dv, self.eps, "sigmoid")
         return ops.linear(y, self.w_out, None, partial_ok=True)

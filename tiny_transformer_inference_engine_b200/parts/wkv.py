@@ -23,15 +23,17 @@ import torch
 from .base import Mixer, ParamSpec, FixedStateNeed, StepContext
 from ..registry import register_part
 
-KEYS_PER_THREAD = 16            # the scan kernels' slice of key channels (csrc/matrix_memory.cu)
+MAX_KEYS = 512                  # key channels per head the scan kernels take (csrc/matrix_memory.cu)
 
 
 def padded_keys(dim: int) -> int:
-    """Key channels of a matrix-state row: a power-of-two number of slices of ``KEYS_PER_THREAD``."""
+    """Key channels of a matrix-state row as the scan kernels lay it out: a power-of-two number of slices of 4 channels
+    (heads of up to 128 key channels), 8 (up to 256) or 16."""
+    per_thread = 4 if dim <= 128 else 8 if dim <= 256 else 16
     slices = 1
-    while slices * KEYS_PER_THREAD < dim:
+    while slices * per_thread < dim:
         slices *= 2
-    return slices * KEYS_PER_THREAD
+    return slices * per_thread
 
 
 @register_part("mixer", "wkv")
@@ -43,8 +45,8 @@ class WKV(Mixer):
         super().__init__(prefix)
         self.d_model, self.num_heads, self.dim, self.eps = int(d_model), int(num_heads), int(dim), float(eps)
         self.decay_rank = -1 if decay_rank is None else int(decay_rank)      # -1: the width of the decay's low-rank path is the weight file's
-        if self.dim > 32 * KEYS_PER_THREAD:
-            raise ValueError(f"wkv: {dim} key channels per head (at most {32 * KEYS_PER_THREAD})")
+        if self.dim > MAX_KEYS:
+            raise ValueError(f"wkv: {dim} key channels per head (at most {MAX_KEYS})")
         self.names = {"mu": "mu", "r": "r", "k": "k", "v": "v", "g": "g", "w1": "w1", "w2": "w2", "w0": "w0", "u": "u",
                       "norm": "norm", "o": "o"}
         if names:
@@ -88,7 +90,7 @@ class WKV(Mixer):
         rkvg = ops.batched_linear(mixes[:4], self.w_rkvg)                                                         # [4, T, H*dim]
         lora = ops.activation(ops.linear(mixes[4], self.w1, None, out_dtype=torch.float32), "tanh", out_dtype=x.dtype)
         wlog = ops.linear(lora, self.w2, None, out_dtype=torch.float32)                                           # [T, H*dim] float32
-        o = ops.wkv_scan(rkvg[0], rkvg[1], rkvg[2], wlog, self.w0, self.u, S.state, x, prev.state, ctx.query_start_loc,
-                         ctx.slot_ids, ctx.num_seqs, H, D)
+        o = ops.wkv_scan(rkvg[0], rkvg[1], rkvg[2], ops.wkv_decay(wlog, self.w0), self.u, S.state, x, prev.state,
+                         ctx.query_start_loc, ctx.slot_ids, ctx.num_seqs, H, D)
         y = ops.head_norm_gate(o, rkvg[3], self.norm_w, H, D, self.eps, "silu")
         return ops.linear(y, self.w_out, None, partial_ok=True)
