@@ -224,6 +224,12 @@ def rel(a, b):
     return ((a.double().cpu() - b.double()).abs().max() / b.double().abs().max()).item()
 
 
+def rel_norm(a, b):
+    """Error in the Frobenius norm: for bfloat16 runs of a recurrence whose read-out divides by a sum that may nearly cancel, where
+    a single element can be off by several roundings while the whole stays close."""
+    return ((a.double().cpu() - b.double()).norm() / b.double().norm()).item()
+
+
 def part_with_weights(category, spec, dtype, ops, seed, scale=0.15, scales=None, tweak=None):
     """The part with random tensors (rounded to the run's dtype where the engine would hold them so) and the same tensors in
     float64 under their relative names.  ``tweak`` may rewrite the tensors before they are loaded."""
@@ -273,6 +279,7 @@ ATTENTION_CASES = {
     "no convolution, no rotation": attn(2, 1, 12, 12, 0.25, window=200, softcap=3.0),
     "window of one, five taps": attn(6, 1, 32, 32, 0.2, conv=5, window=1, rot={"base": 10.0, "dims": 2}),
     "window of a page": attn(2, 2, 8, 20, 0.5, conv=2, window=4, rot={"base": 1000.0, "dims": 4}, softcap=30.0),
+    "sizes of the eight-value kernel": attn(8, 2, 32, 48, 0.3, conv=3, window=23, rot={"base": 200.0, "dims": 16}, softcap=9.0),
 }
 
 
@@ -401,7 +408,10 @@ def test_mlstm_alone(ops, dtype, heads, dim, vdim, cap, S):
             s[3] = 7.0
         outs = run_recurrent(ops, part, xs, cuts, dtype, states, slots=[2, 0])
         for i in range(2):
-            assert rel(outs[i], exps[i]) < (3e-5 if dtype == "float32" else 3e-2), (cuts, i)
+            if dtype == "float32":
+                assert rel(outs[i], exps[i]) < 3e-5, (cuts, i)
+            else:
+                assert rel_norm(outs[i], exps[i]) < 3e-2, (cuts, i)
         assert all(torch.all(s[1] == 0) for s in states)
 
 

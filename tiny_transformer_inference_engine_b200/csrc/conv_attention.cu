@@ -97,6 +97,103 @@ __global__ void __launch_bounds__(128) qkv_conv_rope_store_kernel(const QkvArgs 
     }
 }
 
+// ---- bfloat16, eight values per thread: no shared memory, no barrier, so that prompt portions run as a few waves of threads
+// each with all its loads in flight.  A thread owns eight consecutive values of one head of one token; inside the rotated
+// part it convolves its partner's eight values as well (pairs (i, i + rot/2): the chunk rot/2 away; pairs (2i, 2i + 1): its own).
+// Sizes: D, Dv, Dp and the row stride multiples of 8; rot a multiple of 16 (half pairs) or of 8 (interleaved pairs).
+__device__ __forceinline__ void conv8(const QkvArgs& a, const __nv_bfloat16* __restrict__ proj, const float* __restrict__ tail, int C,
+                                      int t, int j, int c, float* acc) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+    for (int k = 0; k < a.taps; ++k) {
+        const int src = j - (a.taps - 1) + k;
+        float u[8];
+        if (src >= 0) {
+            const uint4 x = *reinterpret_cast<const uint4*>(proj + (size_t)(t - j + src) * a.ld + c);
+            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&x);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(h[i]); u[2 * i] = f.x; u[2 * i + 1] = f.y; }
+        } else {
+            const float* p = tail + (size_t)(a.taps - 1 + src) * C + c;
+            const float4 x = *reinterpret_cast<const float4*>(p), y = *reinterpret_cast<const float4*>(p + 4);
+            u[0] = x.x; u[1] = x.y; u[2] = x.z; u[3] = x.w; u[4] = y.x; u[5] = y.y; u[6] = y.z; u[7] = y.w;
+        }
+        if (a.conv_w) {
+            const float* wp = a.conv_w + (size_t)k * C + c;
+            const float4 w0 = __ldg(reinterpret_cast<const float4*>(wp)), w1 = __ldg(reinterpret_cast<const float4*>(wp + 4));
+            const float w[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[i] = fmaf(w[i], u[i], acc[i]);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[i] = u[i];
+        }
+    }
+}
+
+__global__ void __launch_bounds__(256) qkv_conv_rope_store_vec8_kernel(const QkvArgs a, int T_) {
+    TTIE_PDL_ENTRY();
+    const int chunks = a.Dp >> 3, units = a.Hq + 2 * a.Hkv;
+    const long long id = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (id >= (long long)T_ * units * chunks) return;
+    const int jc = (int)(id % chunks);
+    const int unit = (int)((id / chunks) % units);
+    const int t = (int)(id / ((long long)chunks * units));
+    const int C = a.Hq * a.D + a.Hkv * a.D + a.Hkv * a.Dv;
+    const int kind = unit < a.Hq ? 0 : unit < a.Hq + a.Hkv ? 1 : 2;
+    const int h = kind == 0 ? unit : kind == 1 ? unit - a.Hq : unit - a.Hq - a.Hkv;
+    if (kind != 0 && !a.write_kv) return;
+    const int width = kind == 2 ? a.Dv : a.D;
+    const int c0 = kind == 0 ? h * a.D : kind == 1 ? a.Hq * a.D + h * a.D : (a.Hq + a.Hkv) * a.D + h * a.Dv;
+    const int i0 = jc << 3;                                          // first of this thread's values within the head
+    const __nv_bfloat16* proj = reinterpret_cast<const __nv_bfloat16*>(a.proj);
+    const int s = a.token_seq[t];
+    float out[8];
+    if (i0 >= width) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) out[i] = 0.f;
+    } else {
+        const int j = t - a.qsl[s];
+        const float* tail = a.taps > 1 ? a.tail + (size_t)slot_row_(a.slot_ids[s], a.tail_rows) * (a.taps - 1) * C : nullptr;
+        conv8(a, proj, tail, C, t, j, c0 + i0, out);
+        if (kind != 2 && i0 < a.rot) {
+            const float2* cs = a.cs + (size_t)t * (a.rot >> 1);
+            if (a.style == 1) {
+                const int half = a.rot >> 1;
+                const bool low = i0 < half;
+                float other[8];
+                conv8(a, proj, tail, C, t, j, c0 + (low ? i0 + half : i0 - half), other);
+                const int f0 = low ? i0 : i0 - half;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const float2 c = cs[f0 + i];
+                    out[i] = low ? out[i] * c.x - other[i] * c.y : out[i] * c.x + other[i] * c.y;
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 8; i += 2) {
+                    const float2 c = cs[(i0 + i) >> 1];
+                    const float x = out[i], y = out[i + 1];
+                    out[i] = x * c.x - y * c.y; out[i + 1] = x * c.y + y * c.x;
+                }
+            }
+        }
+    }
+    uint4 packed;
+    __nv_bfloat162* ph = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) ph[i] = __floats2bfloat162_rn(out[2 * i], out[2 * i + 1]);
+    if (kind == 0) {
+        *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.q_out) + ((size_t)t * a.Hq + h) * a.Dp + i0) = packed;
+        return;
+    }
+    const int pos = a.positions[t];
+    int page = a.block_table[(size_t)s * a.table_width + pos / a.page_size];
+    if (page < 0 || page >= a.num_pages) page = 0;                  // validated on the host; never write outside
+    const size_t dst = (((size_t)page * a.Hkv + h) * a.page_size + pos % a.page_size) * a.Dp + i0;
+    *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(kind == 1 ? a.k_pages : a.v_pages) + dst) = packed;
+}
+
 template <typename T>
 __global__ void conv_tail_update_kernel(const T* __restrict__ proj, long long ld, int C, int taps, float* __restrict__ tail,
                                         int tail_rows, const int* __restrict__ qsl, const int* __restrict__ slot_ids) {
@@ -165,6 +262,14 @@ extern "C" int ttie_qkv_conv_rope_store(const void* proj, long long ld, int T, i
     const size_t smem = (size_t)(D > Dv ? D : Dv) * sizeof(float);
     if (T > 2147483647 / 1 || Hq + 2 * Hkv > 65535) TTIE_FAIL("qkv_conv_rope_store: %d heads exceed the grid", Hq + 2 * Hkv);
     cudaStream_t s = (cudaStream_t)stream;
+    const bool aligned = !(((uintptr_t)proj | (uintptr_t)q_out | (uintptr_t)k_pages | (uintptr_t)v_pages | (uintptr_t)conv_w | (uintptr_t)tail) & 15);
+    if (dtype == kBF16 && D % 8 == 0 && Dv % 8 == 0 && Dp % 8 == 0 && ld % 8 == 0 && aligned && (rot == 0 || rot % (style == 1 ? 16 : 8) == 0)) {
+        const long long threads = (long long)T * (Hq + 2 * Hkv) * (Dp / 8);
+        if ((threads + 255) / 256 > 2147483647LL) TTIE_FAIL("qkv_conv_rope_store: grid too large");
+        TTIE_LAUNCH(qkv_conv_rope_store_vec8_kernel, (unsigned)((threads + 255) / 256), 256, 0, s, a, T);
+        TTIE_CHECK_LAUNCH("qkv_conv_rope_store");
+        return 0;
+    }
     dim3 grid(T, Hq + 2 * Hkv);
     if (dtype == kF32) TTIE_LAUNCH(qkv_conv_rope_store_kernel<float>, grid, 128, smem, s, a);
     else if (dtype == kBF16) TTIE_LAUNCH(qkv_conv_rope_store_kernel<__nv_bfloat16>, grid, 128, smem, s, a);

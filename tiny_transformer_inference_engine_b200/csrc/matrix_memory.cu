@@ -138,13 +138,73 @@ __device__ __forceinline__ void stage_rows(E* dst, int dst_ld, const E* src, lon
     }
 }
 
+// KPT consecutive staged values as floats, by vector loads from shared memory
+template <int KPT>
+__device__ __forceinline__ void lds_keys(const float* p, float* o) {
+#pragma unroll
+    for (int i = 0; i < KPT; i += 4) {
+        const float4 x = *reinterpret_cast<const float4*>(p + i);
+        o[i] = x.x; o[i + 1] = x.y; o[i + 2] = x.z; o[i + 3] = x.w;
+    }
+}
+template <int KPT>
+__device__ __forceinline__ void lds_keys(const __nv_bfloat16* p, float* o) {
+#pragma unroll
+    for (int i = 0; i < KPT; i += 4) {
+        const uint2 x = *reinterpret_cast<const uint2*>(p + i);
+        o[i] = __uint_as_float(x.x << 16); o[i + 1] = __uint_as_float(x.x & 0xffff0000u);
+        o[i + 2] = __uint_as_float(x.y << 16); o[i + 3] = __uint_as_float(x.y & 0xffff0000u);
+    }
+}
+
+// Sums over the SL adjacent lanes of a column of CNT values per lane at once (the partial read-outs of a run of tokens): at
+// every step a lane hands half of its values to the partner and adds the partner's other half to the half it keeps, so the
+// run costs CNT - 1 shuffles instead of CNT * log2(SL); once a lane is down to one value the remaining steps are plain
+// butterfly additions.  Afterwards a lane holds, in v[0 ..], the totals of the tokens base, base + 1, ... (max(1, CNT / SL) of them).
+template <int O, int CNT>
+struct RunReduce {
+    static __device__ __forceinline__ void run(float* v, int slice, int& base) {
+        if constexpr (O >= 1) {
+            if constexpr (CNT > 1) {
+                constexpr int HALF = CNT / 2;
+                const bool up = (slice & O) != 0;
+#pragma unroll
+                for (int i = 0; i < HALF; ++i) {
+                    const float send = up ? v[i] : v[i + HALF];
+                    const float keep = up ? v[i + HALF] : v[i];
+                    v[i] = keep + __shfl_xor_sync(0xffffffffu, send, O);
+                }
+                if (up) base += HALF;
+                RunReduce<O / 2, HALF>::run(v, slice, base);
+            } else {
+                v[0] += __shfl_xor_sync(0xffffffffu, v[0], O);
+                RunReduce<O / 2, 1>::run(v, slice, base);
+            }
+        }
+    }
+};
+// tokens a lane holds after RunReduce, and whether it is the one of several equal lanes that writes them
+template <int SL, int N> struct RunOwner {
+    static constexpr int COUNT = N >= SL ? N / SL : 1;
+    static __device__ __forceinline__ bool writes(int slice) { return N >= SL ? true : (slice & (SL / N - 1)) == 0; }
+};
+
+// a request that brings this few tokens (decoded ones) is walked straight from global memory: nothing is staged
+constexpr int DIRECT_TOKENS = 2;
+template <int SL> __device__ __forceinline__ float slices_sum(float v) {
+#pragma unroll
+    for (int o = 1; o < SL; o <<= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
 constexpr int MAXV = 16;            // staged tokens at most; also the most values of v (or gate weights) a thread carries ahead
 
-template <typename T, int KPT>
+template <typename T, int KPT, int SL>
 __global__ void __launch_bounds__(128) wkv_scan_kernel(const WkvArgs a) {
     TTIE_PDL_ENTRY();
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    const int cols = blockDim.x / a.slices, TB = a.tb;
+    constexpr int TB = 64 / KPT;                                     // tokens per stage: 16, 8 or 4
+    const int cols = blockDim.x / SL;
     // two stages of [r | k] in the compute dtype and w in float32, rows of Dpad values; one array of the columns' v
     float* w_s = reinterpret_cast<float*>(smem_raw);                                  // [2][TB][Dpad]
     T* r_s = reinterpret_cast<T*>(w_s + 2 * TB * a.Dpad);                             // [2][TB][Dpad]
@@ -152,7 +212,7 @@ __global__ void __launch_bounds__(128) wkv_scan_kernel(const WkvArgs a) {
     float* v_s = reinterpret_cast<float*>(k_s + 2 * TB * a.Dpad);                     // [TB][cols]
     const int s = blockIdx.z, h = blockIdx.y;
     const int t0 = a.qsl[s], n = a.qsl[s + 1] - t0;
-    const int slice = threadIdx.x % a.slices, cl = threadIdx.x / a.slices;
+    const int slice = threadIdx.x % SL, cl = threadIdx.x / SL;
     const int col = blockIdx.x * cols + cl;
     const bool colv = col < a.D;
     const int HD = a.H * a.D;
@@ -171,6 +231,21 @@ __global__ void __launch_bounds__(128) wkv_scan_kernel(const WkvArgs a) {
     const T* kp = reinterpret_cast<const T*>(a.k) + (size_t)t0 * a.ld + h * a.D;
     const T* vp = reinterpret_cast<const T*>(a.v) + (size_t)t0 * a.ld + h * a.D;
     const float* wp = a.decay + (size_t)t0 * HD + h * a.D;
+    if (n <= DIRECT_TOKENS) {
+        for (int tt = 0; tt < n; ++tt) {
+            const float vj = colv ? to_f32(vp[(size_t)tt * a.ld + col]) : 0.f;
+            float acc = 0.f;
+#pragma unroll
+            for (int i = 0; i < KPT; ++i) {
+                const bool in = ch0 + i < a.D;
+                const float kv = (in ? to_f32(kp[(size_t)tt * a.ld + ch0 + i]) : 0.f) * vj;
+                acc = fmaf(in ? to_f32(rp[(size_t)tt * a.ld + ch0 + i]) : 0.f, fmaf(ub[i], kv, S[i]), acc);
+                S[i] = fmaf(in ? wp[(size_t)tt * HD + ch0 + i] : 0.f, S[i], kv);
+            }
+            acc = slices_sum<SL>(acc);
+            if (slice == 0 && colv) a.out[(size_t)(t0 + tt) * HD + h * a.D + col] = acc;
+        }
+    } else {
     // channels behind D (a head that does not fill its last slice) read as zero in every stage
     if (a.Dpad > a.D)
         for (int e = threadIdx.x; e < 2 * TB * a.Dpad; e += blockDim.x)
@@ -208,19 +283,35 @@ __global__ void __launch_bounds__(128) wkv_scan_kernel(const WkvArgs a) {
         const T* rb = r_s + buf * TB * a.Dpad + ch0;
         const T* kb = k_s + buf * TB * a.Dpad + ch0;
         const float* wb = w_s + buf * TB * a.Dpad + ch0;
-        for (int tt = 0; tt < nb; ++tt) {
-            const float vj = v_s[tt * cols + cl];
-            float acc = 0.f;
+        float part[TB];                                              // this thread's share of every token's read-out
 #pragma unroll
-            for (int i = 0; i < KPT; ++i) {
-                const float kv = to_f32(kb[tt * a.Dpad + i]) * vj;
-                acc = fmaf(to_f32(rb[tt * a.Dpad + i]), fmaf(ub[i], kv, S[i]), acc);
-                S[i] = fmaf(wb[tt * a.Dpad + i], S[i], kv);
+        for (int tt = 0; tt < TB; ++tt) {
+            part[tt] = 0.f;
+            if (tt < nb) {                                           // (the same for every thread of the CTA)
+                const float vj = v_s[tt * cols + cl];
+                float r_[KPT], k_[KPT], w_[KPT];
+                lds_keys<KPT>(rb + tt * a.Dpad, r_);
+                lds_keys<KPT>(kb + tt * a.Dpad, k_);
+                lds_keys<KPT>(wb + tt * a.Dpad, w_);
+                float acc = 0.f;
+#pragma unroll
+                for (int i = 0; i < KPT; ++i) {
+                    const float kv = k_[i] * vj;
+                    acc = fmaf(r_[i], fmaf(ub[i], kv, S[i]), acc);
+                    S[i] = fmaf(w_[i], S[i], kv);
+                }
+                part[tt] = acc;
             }
-            acc = slice_sum(acc, a.slices);
-            if (slice == 0 && colv) a.out[(size_t)(t0 + c0 + tt) * HD + h * a.D + col] = acc;
+        }
+        int first = 0;
+        RunReduce<SL / 2, TB>::run(part, slice, first);
+        if (colv && RunOwner<SL, TB>::writes(slice)) {
+#pragma unroll
+            for (int j = 0; j < RunOwner<SL, TB>::COUNT; ++j)
+                if (first + j < nb) a.out[(size_t)(t0 + c0 + first + j) * HD + h * a.D + col] = part[j];
         }
         __syncthreads();
+    }
     }
     if (colv) {
 #pragma unroll
@@ -235,24 +326,28 @@ __global__ void __launch_bounds__(128) wkv_scan_kernel(const WkvArgs a) {
 
 __device__ __forceinline__ float logsigmoidf_(float x) { return fminf(x, 0.f) - log1pf(expf(-fabsf(x))); }
 
-// The gates of the matrix memory for every token of the step: one warp per (request, head) walks the tokens 32 at a time.
-// With i, f the log gates and F_t the sum of f up to t (from the warp's first token), the running maximum
-// m_t = max(f_t + m_(t-1), i_t) equals F_t + max(m_before, max over s <= t of (i_s - F_s)): a prefix sum and a prefix maximum
-// over the lanes.  Writes per token (state decay e^(f + m_(t-1) - m_t), input weight e^(i - m_t), e^(-m_t)) and moves the
-// request's running maximum in its state row.
-__global__ void __launch_bounds__(32) mlstm_gates_kernel(const float* __restrict__ gates, long long ld_g, float* __restrict__ mx,
-                                                         int state_rows, const int* __restrict__ qsl, const int* __restrict__ slot_ids,
-                                                         float* __restrict__ out, int H, float cap) {
+// The gates of the matrix memory for every token of the step: one CTA of GW warps per (request, head) walks the tokens
+// 32 * GW at a time, a warp per 32 tokens.  With i, f the log gates and F_t the sum of f from a warp's first token to t, the
+// running maximum m_t = max(f_t + m_(t-1), i_t) equals F_t + max(m_in, max over s <= t of (i_s - F_s)): a prefix sum and a
+// prefix maximum over the lanes; a warp's m_in follows from the warps before it by the same rule applied to their totals.
+// Writes per token (state decay e^(f + m_(t-1) - m_t), input weight e^(i - m_t), e^(-m_t)) and moves the request's running
+// maximum in its state row.
+constexpr int GW = 8;
+__global__ void __launch_bounds__(32 * GW) mlstm_gates_kernel(const float* __restrict__ gates, long long ld_g, float* __restrict__ mx,
+                                                              int state_rows, const int* __restrict__ qsl, const int* __restrict__ slot_ids,
+                                                              float* __restrict__ out, int H, float cap) {
     TTIE_PDL_ENTRY();
-    const int s = blockIdx.y, h = blockIdx.x, lane = threadIdx.x;
+    __shared__ float tot_f[GW], tot_x[GW], carry;
+    const int s = blockIdx.y, h = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int t0 = qsl[s], n = qsl[s + 1] - t0;
     float* mrow = mx + (size_t)slot_row_(slot_ids[s], state_rows) * H + h;
-    float m = *mrow;
-    for (int c0 = 0; c0 < n; c0 += 32) {
-        const bool valid = c0 + lane < n;
+    if (threadIdx.x == 0) carry = *mrow;
+    for (int c0 = 0; c0 < n; c0 += 32 * GW) {
+        const int t = c0 + warp * 32 + lane;
+        const bool valid = t < n;
         float ig = -INFINITY, fg = 0.f;
         if (valid) {
-            const float* g = gates + (size_t)(t0 + c0 + lane) * ld_g;
+            const float* g = gates + (size_t)(t0 + t) * ld_g;
             ig = cap * tanhf(g[h] / cap);
             fg = logsigmoidf_(cap * tanhf(g[H + h] / cap));
         }
@@ -262,16 +357,22 @@ __global__ void __launch_bounds__(32) mlstm_gates_kernel(const float* __restrict
         float X = ig - F;
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) { const float y = __shfl_up_sync(0xffffffffu, X, o); if (lane >= o) X = fmaxf(X, y); }
-        const float m_t = F + fmaxf(m, X);
+        if (lane == 31) { tot_f[warp] = F; tot_x[warp] = X; }
+        __syncthreads();
+        float m_in = carry;
+        for (int w = 0; w < warp; ++w) m_in = tot_f[w] + fmaxf(m_in, tot_x[w]);
+        const float m_t = F + fmaxf(m_in, X);
         float m_prev = __shfl_up_sync(0xffffffffu, m_t, 1);
-        if (lane == 0) m_prev = m;
+        if (lane == 0) m_prev = m_in;
         if (valid) {
-            float* o3 = out + ((size_t)(t0 + c0 + lane) * H + h) * 3;
+            float* o3 = out + ((size_t)(t0 + t) * H + h) * 3;
             o3[0] = expf(fg + m_prev - m_t); o3[1] = expf(ig - m_t); o3[2] = expf(-m_t);
         }
-        m = __shfl_sync(0xffffffffu, m_t, min(31, n - c0 - 1));
+        __syncthreads();
+        if (warp == GW - 1 && lane == 31) carry = m_t;               // (lanes behind the last token pass the maximum on unchanged)
+        __syncthreads();
     }
-    if (lane == 0) *mrow = m;
+    if (threadIdx.x == 0) *mrow = carry;
 }
 
 struct MlstmArgs {
@@ -283,18 +384,19 @@ struct MlstmArgs {
     int H, D, Dv, Dpad, slices, tb; float qscale; bool vec;
 };
 
-template <typename T, int KPT>
+template <typename T, int KPT, int SL>
 __global__ void __launch_bounds__(128) mlstm_scan_kernel(const MlstmArgs a) {
     TTIE_PDL_ENTRY();
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    const int cols = blockDim.x / a.slices, TB = a.tb;
+    constexpr int TB = 64 / KPT;
+    const int cols = blockDim.x / SL;
     T* q_s = reinterpret_cast<T*>(smem_raw);                                          // [2][TB][Dpad]
     T* k_s = q_s + 2 * TB * a.Dpad;
     float* v_s = reinterpret_cast<float*>(k_s + 2 * TB * a.Dpad);                     // [TB][cols]
     float* g_s = v_s + TB * cols;                                                     // [TB][3]: state decay, input weight, e^(-m)
     const int s = blockIdx.z, h = blockIdx.y;
     const int t0 = a.qsl[s], n = a.qsl[s + 1] - t0;
-    const int slice = threadIdx.x % a.slices, cl = threadIdx.x / a.slices;
+    const int slice = threadIdx.x % SL, cl = threadIdx.x / SL;
     const int col = blockIdx.x * cols + cl;
     const bool colv = col < a.Dv;
     const int ch0 = slice * KPT;
@@ -313,6 +415,26 @@ __global__ void __launch_bounds__(128) mlstm_scan_kernel(const MlstmArgs a) {
     const T* kp = reinterpret_cast<const T*>(a.k) + (size_t)t0 * a.ld + h * a.D;
     const T* vp = reinterpret_cast<const T*>(a.v) + (size_t)t0 * a.ld + h * a.Dv;
     const float* gp = a.gates + ((size_t)t0 * a.H + h) * 3;
+    if (n <= DIRECT_TOKENS) {
+        for (int tt = 0; tt < n; ++tt) {
+            const float vj = colv ? to_f32(vp[(size_t)tt * a.ld + col]) : 0.f;
+            const float fa = gp[(size_t)tt * a.H * 3], ib = gp[(size_t)tt * a.H * 3 + 1], em = gp[(size_t)tt * a.H * 3 + 2];
+            float num = 0.f, nq = 0.f;
+#pragma unroll
+            for (int i = 0; i < KPT; ++i) {
+                const bool in = ch0 + i < a.D;
+                const float bk = ib * (in ? to_f32(kp[(size_t)tt * a.ld + ch0 + i]) : 0.f);
+                const float qv = (in ? to_f32(qp[(size_t)tt * a.ld + ch0 + i]) : 0.f) * a.qscale;
+                S[i] = fmaf(fa, S[i], bk * vj);
+                nv[i] = fmaf(fa, nv[i], bk);
+                num = fmaf(S[i], qv, num);
+                nq = fmaf(nv[i], qv, nq);
+            }
+            num = slices_sum<SL>(num);
+            nq = slices_sum<SL>(nq);
+            if (slice == 0 && colv) a.out[(size_t)(t0 + tt) * a.H * a.Dv + h * a.Dv + col] = num / (fmaxf(fabsf(nq), em) + 1e-6f);
+        }
+    } else {
     if (a.Dpad > a.D)
         for (int e = threadIdx.x; e < 2 * TB * a.Dpad; e += blockDim.x)
             if (e % a.Dpad >= a.D) { q_s[e] = from_f32<T>(0.f); k_s[e] = from_f32<T>(0.f); }
@@ -357,25 +479,41 @@ __global__ void __launch_bounds__(128) mlstm_scan_kernel(const MlstmArgs a) {
         __syncthreads();
         const T* qb = q_s + buf * TB * a.Dpad + ch0;
         const T* kb = k_s + buf * TB * a.Dpad + ch0;
-        for (int tt = 0; tt < nb; ++tt) {
-            const float vj = v_s[tt * cols + cl];
-            const float fa = g_s[3 * tt], ib = g_s[3 * tt + 1];
-            float num = 0.f, nq = 0.f;
+        float pnum[TB], pden[TB];                                    // this thread's share of every token's S^T q and n . q
 #pragma unroll
-            for (int i = 0; i < KPT; ++i) {
-                const float bk = ib * to_f32(kb[tt * a.Dpad + i]);
-                const float qv = to_f32(qb[tt * a.Dpad + i]) * a.qscale;
-                S[i] = fmaf(fa, S[i], bk * vj);
-                nv[i] = fmaf(fa, nv[i], bk);
-                num = fmaf(S[i], qv, num);
-                nq = fmaf(nv[i], qv, nq);
+        for (int tt = 0; tt < TB; ++tt) {
+            pnum[tt] = 0.f; pden[tt] = 0.f;
+            if (tt < nb) {                                           // (the same for every thread of the CTA)
+                const float vj = v_s[tt * cols + cl];
+                const float fa = g_s[3 * tt], ib = g_s[3 * tt + 1];
+                float q_[KPT], k_[KPT];
+                lds_keys<KPT>(qb + tt * a.Dpad, q_);
+                lds_keys<KPT>(kb + tt * a.Dpad, k_);
+                float num = 0.f, nq = 0.f;
+#pragma unroll
+                for (int i = 0; i < KPT; ++i) {
+                    const float bk = ib * k_[i];
+                    const float qv = q_[i] * a.qscale;
+                    S[i] = fmaf(fa, S[i], bk * vj);
+                    nv[i] = fmaf(fa, nv[i], bk);
+                    num = fmaf(S[i], qv, num);
+                    nq = fmaf(nv[i], qv, nq);
+                }
+                pnum[tt] = num; pden[tt] = nq;
             }
-            num = slice_sum(num, a.slices);
-            nq = slice_sum(nq, a.slices);
-            if (slice == 0 && colv)
-                a.out[(size_t)(t0 + c0 + tt) * a.H * a.Dv + h * a.Dv + col] = num / (fmaxf(fabsf(nq), g_s[3 * tt + 2]) + 1e-6f);
+        }
+        int first = 0, first2 = 0;
+        RunReduce<SL / 2, TB>::run(pnum, slice, first);
+        RunReduce<SL / 2, TB>::run(pden, slice, first2);
+        if (colv && RunOwner<SL, TB>::writes(slice)) {
+#pragma unroll
+            for (int j = 0; j < RunOwner<SL, TB>::COUNT; ++j)
+                if (first + j < nb)
+                    a.out[(size_t)(t0 + c0 + first + j) * a.H * a.Dv + h * a.Dv + col] =
+                        pnum[j] / (fmaxf(fabsf(pden[j]), g_s[3 * (first + j) + 2]) + 1e-6f);
         }
         __syncthreads();
+    }
     }
     if (colv) {
 #pragma unroll
@@ -446,7 +584,7 @@ extern "C" int ttie_wkv_decay(const float* wlog, long long ld, const float* w0, 
 extern "C" int ttie_mlstm_gates(const float* gates, long long ld_g, float* mx, int state_rows, const int* qsl, const int* slot_ids,
                                 int num_seqs, float* out, int H, float cap, void* stream) {
     if (num_seqs <= 0) return 0;
-    TTIE_LAUNCH(mlstm_gates_kernel, dim3(H, num_seqs), 32, 0, (cudaStream_t)stream, gates, ld_g, mx, state_rows, qsl, slot_ids, out, H, cap);
+    TTIE_LAUNCH(mlstm_gates_kernel, dim3(H, num_seqs), 32 * GW, 0, (cudaStream_t)stream, gates, ld_g, mx, state_rows, qsl, slot_ids, out, H, cap);
     TTIE_CHECK_LAUNCH("mlstm_gates");
     return 0;
 }
@@ -470,21 +608,25 @@ extern "C" int ttie_token_shift_mix(const void* x, long long ld, int T, int d, i
     return 0;
 }
 
-template <typename T, int KPT, typename Args>
+template <typename Args>
 int launch_scan(void (*kernel)(const Args), const Args& a, dim3 grid, int threads, size_t smem, cudaStream_t s) {
     if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);   // (wide heads)
     return TTIE_LAUNCH(kernel, grid, threads, smem, s, a) == cudaSuccess ? 0 : -1;
 }
 
-#define TTIE_SCAN_DISPATCH(KERNEL, ARGS)                                                                            \
-    do {                                                                                                            \
-        if (dtype != kF32 && dtype != kBF16) TTIE_FAIL(#KERNEL ": unknown dtype %d", dtype);                         \
-        if (kpt == 4) { if (dtype == kF32) launch_scan<float, 4, ARGS>(KERNEL<float, 4>, a, grid, threads, smem, s); \
-                        else launch_scan<__nv_bfloat16, 4, ARGS>(KERNEL<__nv_bfloat16, 4>, a, grid, threads, smem, s); } \
-        else if (kpt == 8) { if (dtype == kF32) launch_scan<float, 8, ARGS>(KERNEL<float, 8>, a, grid, threads, smem, s); \
-                             else launch_scan<__nv_bfloat16, 8, ARGS>(KERNEL<__nv_bfloat16, 8>, a, grid, threads, smem, s); } \
-        else { if (dtype == kF32) launch_scan<float, 16, ARGS>(KERNEL<float, 16>, a, grid, threads, smem, s);        \
-               else launch_scan<__nv_bfloat16, 16, ARGS>(KERNEL<__nv_bfloat16, 16>, a, grid, threads, smem, s); }   \
+// the kernel for a dtype, a number of key channels per thread and a number of slices (those of scan_shape: 4 channels with
+// 1 to 32 slices, 8 or 16 channels with 32)
+#define TTIE_SCAN_CASE(KERNEL, ARGS, K, L)                                                                            \
+    if (kpt == K && a.slices == L) {                                                                                  \
+        if (dtype == kF32) launch_scan<ARGS>(KERNEL<float, K, L>, a, grid, threads, smem, s);                        \
+        else launch_scan<ARGS>(KERNEL<__nv_bfloat16, K, L>, a, grid, threads, smem, s);                              \
+    }
+#define TTIE_SCAN_DISPATCH(KERNEL, ARGS)                                                                              \
+    do {                                                                                                              \
+        if (dtype != kF32 && dtype != kBF16) TTIE_FAIL(#KERNEL ": unknown dtype %d", dtype);                           \
+        TTIE_SCAN_CASE(KERNEL, ARGS, 4, 1) TTIE_SCAN_CASE(KERNEL, ARGS, 4, 2) TTIE_SCAN_CASE(KERNEL, ARGS, 4, 4)       \
+        TTIE_SCAN_CASE(KERNEL, ARGS, 4, 8) TTIE_SCAN_CASE(KERNEL, ARGS, 4, 16) TTIE_SCAN_CASE(KERNEL, ARGS, 4, 32)     \
+        TTIE_SCAN_CASE(KERNEL, ARGS, 8, 32) TTIE_SCAN_CASE(KERNEL, ARGS, 16, 32)                                       \
     } while (0)
 
 extern "C" int ttie_wkv_scan(const void* r, const void* k, const void* v, long long ld, const float* decay, const float* u, float* state,
@@ -500,7 +642,7 @@ extern "C" int ttie_wkv_scan(const void* r, const void* k, const void* v, long l
     a.Dpad = a.slices * kpt;
     const int cols = threads / a.slices;
     const int es = dtype == kF32 ? 4 : 2, ce = 16 / es;                // bytes per value of r and k; values per 16-byte copy
-    a.tb = a.Dpad <= 128 ? 16 : a.Dpad <= 256 ? 8 : 4;
+    a.tb = 64 / kpt;
     if (threads * MAXV < a.tb * cols) TTIE_FAIL("wkv_scan: internal: %d threads cannot carry %d x %d values", threads, a.tb, cols);
     const size_t smem = (size_t)2 * a.tb * a.Dpad * (4 + 2 * es) + (size_t)a.tb * cols * 4;
     a.vec = D % ce == 0 && D % 4 == 0 && ld % ce == 0 && !(((uintptr_t)r | (uintptr_t)k | (uintptr_t)decay) & 15);
@@ -523,7 +665,7 @@ extern "C" int ttie_mlstm_scan(const void* q, const void* k, const void* v, long
     a.Dpad = a.slices * kpt;
     const int cols = threads / a.slices;
     const int es = dtype == kF32 ? 4 : 2, ce = 16 / es;
-    a.tb = a.Dpad <= 128 ? 16 : a.Dpad <= 256 ? 8 : 4;
+    a.tb = 64 / kpt;
     if (threads * MAXV < a.tb * cols || 2 * threads < a.tb * 3) TTIE_FAIL("mlstm_scan: internal: %d threads cannot carry %d x %d values", threads, a.tb, cols);
     const size_t smem = (size_t)2 * a.tb * a.Dpad * 2 * es + (size_t)a.tb * (cols + 3) * 4;
     a.vec = D % ce == 0 && ld % ce == 0 && !(((uintptr_t)q | (uintptr_t)k) & 15);
