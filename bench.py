@@ -372,7 +372,7 @@ def op_cost(name, args, kw, out, kv_lens, window):
             r, state, n, H, D = args[0], args[5], args[10], args[11], args[12]
             T, per_tok, fma = r.shape[0], 3 * H * D * r.element_size() + 8 * H * D, 3 * H * D * D
         else:
-            q, state, n, H, D, Dv = args[0], args[4], args[8], args[9], args[10], args[11]
+            q, state, n, H, D, Dv = args[0], args[4], args[9], args[10], args[11], args[12]
             T, per_tok, fma = q.shape[0], (2 * H * D + H * Dv) * q.element_size() + 4 * H * Dv + 8 * H, 4 * H * D * Dv
         row = state[0].numel() * 4
         return T * per_tok + 2 * n * row, ("fp32", 2 * T * fma)

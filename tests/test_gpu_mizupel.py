@@ -462,3 +462,30 @@ def test_first_tokens_of_a_sequence():
     eng = engine_for(cfg, w, "float32", pages=40, max_seqs=6)
     check(tu.run_steps(eng, tu.whole(reqs)), exp, "float32")
     check(tu.run_steps(eng, tu.prefill_then_decode(reqs, tail=5)), exp, "float32")
+
+
+def test_the_scan_reads_the_normaliser_copy_not_the_row_it_writes(ops):
+    """One CTA of a head writes the head's new normaliser state while the head's other CTAs may not have started: they must
+    read the copy made before the step.  With the state row overwritten by nonsense after the copy was made, a one-token step
+    and a long step must give the same read-outs and leave the same state as an undisturbed run."""
+    H, D, Dv, slots = 2, 32, 64, 3
+    P = ops.matrix_state_pad(D)
+    g = torch.Generator().manual_seed(3)
+    for n_tok in (1, 40):
+        qkv = (torch.randn(n_tok, 2 * H * D + H * Dv, generator=g) * 0.5).to(DEV)
+        q, k, v = qkv[:, :H * D], qkv[:, H * D:2 * H * D], qkv[:, 2 * H * D:]
+        pre = (torch.randn(n_tok, 2 * H, generator=g) * 2).to(DEV)
+        qsl = torch.tensor([0, n_tok], dtype=torch.int32, device=DEV)
+        slot = torch.tensor([1], dtype=torch.int32, device=DEV)
+        results = []
+        for disturb in (False, True):
+            S = (torch.randn(slots + 1, H, Dv, P, generator=torch.Generator().manual_seed(5)) * 0.3).to(DEV)
+            n = (torch.randn(slots + 1, H, P, generator=torch.Generator().manual_seed(6)) * 0.3).to(DEV)
+            m = torch.full((slots + 1, H), 0.7, device=DEV)
+            w, before = ops.mlstm_gates(pre, m, n, qsl, slot, 1, H, 6.0)
+            if disturb:
+                n[1] = 1e6
+            o = ops.mlstm_scan(q, k, v, w, S, n, before, qsl, slot, 1, H, D, Dv, D ** -0.5)
+            results.append((o.cpu(), n[1].cpu().clone(), S[1].cpu().clone()))
+        for a, b in zip(*results):
+            assert torch.equal(a, b)

@@ -18,7 +18,7 @@
 //   wkv_scan          o_t = (S + diag(u) k_t v_t^T)^T r_t, then S <- diag(w_t) S + k_t v_t^T;
 //                     also stores the request's last mixer input as the next step's previous token
 //   mlstm_gates       i = cap tanh(i'/cap), f = logsigmoid(cap tanh(f'/cap)), m' = max(f + m, i) as prefix operations of a warp;
-//                     per token e^(f+m-m'), e^(i-m'), e^(-m')
+//                     per token e^(f+m-m'), e^(i-m'), e^(-m'); also copies the normaliser state n for the scan to read
 //   mlstm_scan        S <- e^(f+m-m') S + e^(i-m') k v^T, n likewise with k alone, o = S^T q / (max(|n.q|, e^(-m')) + 1e-6)
 //   head_norm_gate    out = o / rms(o over the head) * weight * act(gate)   (act: silu or sigmoid)
 #include "common.cuh"
@@ -335,11 +335,16 @@ __device__ __forceinline__ float logsigmoidf_(float x) { return fminf(x, 0.f) - 
 constexpr int GW = 8;
 __global__ void __launch_bounds__(32 * GW) mlstm_gates_kernel(const float* __restrict__ gates, long long ld_g, float* __restrict__ mx,
                                                               int state_rows, const int* __restrict__ qsl, const int* __restrict__ slot_ids,
-                                                              float* __restrict__ out, int H, float cap) {
+                                                              float* __restrict__ out, int H, float cap,
+                                                              const float* __restrict__ nrm, float* __restrict__ nsnap, int Dpad) {
     TTIE_PDL_ENTRY();
     __shared__ float tot_f[GW], tot_x[GW], carry;
     const int s = blockIdx.y, h = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int t0 = qsl[s], n = qsl[s + 1] - t0;
+    // a copy of the head's normaliser state as it stands before this step: the scan's CTAs all read it while one of them
+    // writes the new one into the state row, which a CTA that starts late must not see
+    for (int i = threadIdx.x; i < Dpad; i += blockDim.x)
+        nsnap[((size_t)s * H + h) * Dpad + i] = nrm[((size_t)slot_row_(slot_ids[s], state_rows) * H + h) * Dpad + i];
     float* mrow = mx + (size_t)slot_row_(slot_ids[s], state_rows) * H + h;
     if (threadIdx.x == 0) carry = *mrow;
     for (int c0 = 0; c0 < n; c0 += 32 * GW) {
@@ -379,6 +384,7 @@ struct MlstmArgs {
     const void* q; const void* k; const void* v; long long ld;        // q, k [T, H*D]; v [T, H*Dv]; one row stride
     const float* gates;                                               // [T, H, 3] from mlstm_gates
     float* S; float* nrm; int state_rows;                             // [rows, H, Dv, Dpad], [rows, H, Dpad]
+    const float* nsnap;                                               // [requests, H, Dpad]: n as it stood before the step (mlstm_gates)
     const int* qsl; const int* slot_ids;
     float* out;                                                       // [T, H*Dv] float32
     int H, D, Dv, Dpad, slices, tb; float qscale; bool vec;
@@ -408,7 +414,7 @@ __global__ void __launch_bounds__(128) mlstm_scan_kernel(const MlstmArgs a) {
     for (int i = 0; i < KPT; i += 4) {
         const float4 x4 = colv ? *reinterpret_cast<const float4*>(sp + i) : make_float4(0.f, 0.f, 0.f, 0.f);
         S[i] = x4.x; S[i + 1] = x4.y; S[i + 2] = x4.z; S[i + 3] = x4.w;
-        const float4 n4 = *reinterpret_cast<const float4*>(np + i);
+        const float4 n4 = *reinterpret_cast<const float4*>(a.nsnap + ((size_t)s * a.H + h) * a.Dpad + ch0 + i);
         nv[i] = n4.x; nv[i + 1] = n4.y; nv[i + 2] = n4.z; nv[i + 3] = n4.w;
     }
     const T* qp = reinterpret_cast<const T*>(a.q) + (size_t)t0 * a.ld + h * a.D;
@@ -582,9 +588,10 @@ extern "C" int ttie_wkv_decay(const float* wlog, long long ld, const float* w0, 
 }
 
 extern "C" int ttie_mlstm_gates(const float* gates, long long ld_g, float* mx, int state_rows, const int* qsl, const int* slot_ids,
-                                int num_seqs, float* out, int H, float cap, void* stream) {
+                                int num_seqs, float* out, int H, float cap, const float* nrm, float* nsnap, int Dpad, void* stream) {
     if (num_seqs <= 0) return 0;
-    TTIE_LAUNCH(mlstm_gates_kernel, dim3(H, num_seqs), 32 * GW, 0, (cudaStream_t)stream, gates, ld_g, mx, state_rows, qsl, slot_ids, out, H, cap);
+    TTIE_LAUNCH(mlstm_gates_kernel, dim3(H, num_seqs), 32 * GW, 0, (cudaStream_t)stream, gates, ld_g, mx, state_rows, qsl, slot_ids, out, H, cap,
+                nrm, nsnap, Dpad);
     TTIE_CHECK_LAUNCH("mlstm_gates");
     return 0;
 }
@@ -654,11 +661,11 @@ extern "C" int ttie_wkv_scan(const void* r, const void* k, const void* v, long l
 }
 
 extern "C" int ttie_mlstm_scan(const void* q, const void* k, const void* v, long long ld, const float* gates, float* S, float* nrm,
-                               int state_rows, const int* qsl, const int* slot_ids, int num_seqs, float* out, int H, int D, int Dv,
+                               const float* nsnap, int state_rows, const int* qsl, const int* slot_ids, int num_seqs, float* out, int H, int D, int Dv,
                                float qscale, int dtype, void* stream) {
     if (num_seqs <= 0) return 0;
     MlstmArgs a;
-    a.q = q; a.k = k; a.v = v; a.ld = ld; a.gates = gates; a.S = S; a.nrm = nrm; a.state_rows = state_rows;
+    a.q = q; a.k = k; a.v = v; a.ld = ld; a.gates = gates; a.S = S; a.nrm = nrm; a.nsnap = nsnap; a.state_rows = state_rows;
     a.qsl = qsl; a.slot_ids = slot_ids; a.out = out; a.H = H; a.D = D; a.Dv = Dv; a.qscale = qscale;
     int threads, kpt;
     if (scan_shape(D, Dv, num_seqs * H, &kpt, &a.slices, &threads)) TTIE_FAIL("mlstm_scan: %d key channels per head (at most 512)", D);

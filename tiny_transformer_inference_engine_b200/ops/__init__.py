@@ -86,8 +86,9 @@ _SIGNATURES = {
     "ttie_wkv_decay": [_c_void, _c_ll, _c_void, _c_void, _c_int, _c_int, _c_void],
     "ttie_wkv_scan": [_c_void, _c_void, _c_void, _c_ll, _c_void, _c_void, _c_void, _c_int, _c_void, _c_ll, _c_int, _c_void,
                       _c_int, _c_void, _c_void, _c_int, _c_void, _c_int, _c_int, _c_int, _c_void],
-    "ttie_mlstm_gates": [_c_void, _c_ll, _c_void, _c_int, _c_void, _c_void, _c_int, _c_void, _c_int, _c_float, _c_void],
-    "ttie_mlstm_scan": [_c_void, _c_void, _c_void, _c_ll, _c_void, _c_void, _c_void, _c_int, _c_void, _c_void, _c_int,
+    "ttie_mlstm_gates": [_c_void, _c_ll, _c_void, _c_int, _c_void, _c_void, _c_int, _c_void, _c_int, _c_float, _c_void, _c_void, _c_int,
+                         _c_void],
+    "ttie_mlstm_scan": [_c_void, _c_void, _c_void, _c_ll, _c_void, _c_void, _c_void, _c_void, _c_int, _c_void, _c_void, _c_int,
                         _c_void, _c_int, _c_int, _c_int, _c_float, _c_int, _c_void],
     "ttie_head_norm_gate": [_c_void, _c_void, _c_ll, _c_void, _c_int, _c_int, _c_int, _c_float, _c_int, _c_void, _c_int, _c_void],
     "ttie_activation": [_c_void, _c_void, _c_ll, _c_int, _c_float, _c_int, _c_int, _c_void],
@@ -1025,26 +1026,30 @@ class CudaOps:
         self.launches += 1
         return out
 
-    def mlstm_gates(self, pre, m, query_start_loc, slot_ids, num_seqs, num_heads, cap):
+    def mlstm_gates(self, pre, m, n, query_start_loc, slot_ids, num_seqs, num_heads, cap):
         """Per token and head (state decay, input weight, exp(-running maximum)) from the gate pre-activations ``pre`` float32
         [T, 2H] (input gate's, then forget gate's), with log gates capped at ``cap``; the running maximum of every request
-        moves in its row of ``m`` [slots + 1, H].  Returns float32 [T, H, 3]."""
+        moves in its row of ``m`` [slots + 1, H].  Also copies every request's normaliser state out of ``n``
+        [slots + 1, H, padded dim] as it stands before the step.  Returns (float32 [T, H, 3], the copy [requests, H, padded dim])."""
         T = pre.shape[0]
         out = torch.empty((T, num_heads, 3), dtype=torch.float32, device=pre.device)
+        snap = torch.empty((int(num_seqs), num_heads, n.shape[-1]), dtype=torch.float32, device=pre.device)
         self._check(self.lib.ttie_mlstm_gates(_ptr(pre), pre.stride(0), _ptr(m), m.shape[0], _ptr(query_start_loc), _ptr(slot_ids),
-                                              int(num_seqs), _ptr(out), num_heads, float(cap), self._stream(pre)), "mlstm_gates")
+                                              int(num_seqs), _ptr(out), num_heads, float(cap), _ptr(n), _ptr(snap), n.shape[-1],
+                                              self._stream(pre)), "mlstm_gates")
         self.launches += 1
-        return out
+        return out, snap
 
-    def mlstm_scan(self, q, k, v, gates, S, n, query_start_loc, slot_ids, num_seqs, num_heads, dim, v_dim, q_scale):
-        """The matrix memory's recurrence over the step's tokens from the state rows S [slots + 1, H, v_dim, padded dim] and
-        n [slots + 1, H, padded dim] (advanced in place).  q, k [T, H*dim], v [T, H*v_dim]: views with one row stride;
-        ``gates`` from ``mlstm_gates``.  Returns o float32 [T, H*v_dim]."""
+    def mlstm_scan(self, q, k, v, gates, S, n, n_before, query_start_loc, slot_ids, num_seqs, num_heads, dim, v_dim, q_scale):
+        """The matrix memory's recurrence over the step's tokens from the state rows S [slots + 1, H, v_dim, padded dim] (advanced
+        in place) and from ``n_before``, the copy of the normaliser state that ``mlstm_gates`` made (the new one is written
+        into ``n`` [slots + 1, H, padded dim]).  q, k [T, H*dim], v [T, H*v_dim]: views with one row stride; ``gates`` from
+        ``mlstm_gates``.  Returns o float32 [T, H*v_dim]."""
         T = q.shape[0]
         out = torch.empty((T, num_heads * v_dim), dtype=torch.float32, device=q.device)
         if not (q.stride(0) == k.stride(0) == v.stride(0)):
             raise KernelError("mlstm_scan: q, k and v must share a row stride")
-        self._check(self.lib.ttie_mlstm_scan(_ptr(q), _ptr(k), _ptr(v), q.stride(0), _ptr(gates), _ptr(S), _ptr(n),
+        self._check(self.lib.ttie_mlstm_scan(_ptr(q), _ptr(k), _ptr(v), q.stride(0), _ptr(gates), _ptr(S), _ptr(n), _ptr(n_before),
                                              S.shape[0], _ptr(query_start_loc), _ptr(slot_ids), int(num_seqs), _ptr(out), num_heads,
                                              dim, v_dim, float(q_scale), self._dt(q), self._stream(q)), "mlstm_scan")
         self.launches += 1

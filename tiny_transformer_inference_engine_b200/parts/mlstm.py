@@ -74,8 +74,8 @@ class MLSTM(Mixer):
         proj = ops.linear(x, self.w_in, None)                                                  # [T, q | k | v | g]
         gates = ops.linear(x, self.w_gates, self.b_gates, out_dtype=torch.float32)             # [T, 2H] float32
         q, k, v, g = proj[:, :H * D], proj[:, H * D:2 * H * D], proj[:, 2 * H * D:2 * H * D + H * Dv], proj[:, 2 * H * D + H * Dv:]
-        weights = ops.mlstm_gates(gates, mx.state, ctx.query_start_loc, ctx.slot_ids, ctx.num_seqs, H, self.gate_cap)
-        o = ops.mlstm_scan(q, k, v, weights, S.state, nrm.state, ctx.query_start_loc, ctx.slot_ids, ctx.num_seqs,
+        weights, n_before = ops.mlstm_gates(gates, mx.state, nrm.state, ctx.query_start_loc, ctx.slot_ids, ctx.num_seqs, H, self.gate_cap)
+        o = ops.mlstm_scan(q, k, v, weights, S.state, nrm.state, n_before, ctx.query_start_loc, ctx.slot_ids, ctx.num_seqs,
                            H, D, Dv, D ** -0.5)
         y = ops.head_norm_gate(o, g, self.norm_w, H, Dv, self.eps, "sigmoid")
         return ops.linear(y, self.w_out, None, partial_ok=True)
