@@ -67,7 +67,8 @@ def rotate(x, rot, first_position=0):
 
 def attention(h, W, p, m):
     S = h.shape[0]
-    H, G, D, Dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+    H, D = m["heads"], m["dim"]
+    G, Dv = m.get("kv_heads", H), m.get("vdim", D)
     q = h @ W[p + "q"].T + W[p + "q.b"]
     k = h @ W[p + "k"].T + W[p + "k.b"]
     v = h @ W[p + "v"].T + W[p + "v.b"]

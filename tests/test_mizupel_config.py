@@ -35,7 +35,7 @@ def test_config_is_picked_by_architecture_and_round_trips(tmp_path):
     (lambda c: c["layers"][1]["mixer"].pop("gate_cap"), "gate_cap"),
     (lambda c: c["layers"][3].update(weights_of=3), "another layer"),
     (lambda c: c["layers"][4].update(weights_of=3), "owns no tensors"),
-    (lambda c: c["layers"][3].update(weights_of=2), "must equal"),
+    (lambda c: c["layers"][3].update(weights_of=2), "type"),
     (lambda c: c["layers"][0]["mlp"].update(kind="moe"), "unknown"),
     (lambda c: c.update(logit_softcap=-1.0), "logit_softcap"),
     (lambda c: c.pop("norm"), "norm"),

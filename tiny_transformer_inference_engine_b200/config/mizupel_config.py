@@ -4,7 +4,7 @@ config.json keys: ``architecture`` ("Mizupel"), ``vocab``, ``width``, ``norm.eps
 none) and ``layers``, a list with one entry per layer: ``type`` (the mixer: ``attention``, ``wkv`` or ``mlstm``), ``mixer``
 (its sizes and constants), ``mlp`` (``kind`` ``dense`` with ``ff``, or null / absent for a layer without a feed-forward) and
 optionally ``weights_of``: j, a layer that owns no tensors and runs layer j's (mixer, feed-forward and norms) with a cache or
-state of its own; the rest of such an entry must equal layer j's.  Every size and every constant that can differ between
+state of its own; such an entry is of layer j's type and layer j's sizes and constants are the ones that run.  Every size and every constant that can differ between
 models is read from there; nothing has a default in code.  The design names no longest sequence; ``max_seq_len`` is this
 engine's own bound on positions (an optional key, else ``DEFAULT_MAX_SEQ_LEN``).
 """
@@ -52,10 +52,11 @@ class MizupelConfig:
             _need(L, ("type", "mixer"), where)
             m = L["mixer"]
             if L["type"] == "attention":
-                _need(m, ("heads", "kv_heads", "dim", "vdim", "scale"), f"{where}.mixer")
+                _need(m, ("heads", "dim", "scale"), f"{where}.mixer")          # (kv_heads absent: one per head; vdim absent: dim)
                 for k in ("heads", "kv_heads", "dim", "vdim"):
-                    _pos_int(m[k], f"{where}.mixer.{k}")
-                if m["heads"] % m["kv_heads"]:
+                    if k in m:
+                        _pos_int(m[k], f"{where}.mixer.{k}")
+                if m["heads"] % m.get("kv_heads", m["heads"]):
                     raise ConfigError(f"{where}.mixer: {m['heads']} heads are not a multiple of {m['kv_heads']} kv_heads")
                 _pos_num(m["scale"], f"{where}.mixer.scale")
                 if m.get("conv") is not None:
@@ -105,8 +106,8 @@ class MizupelConfig:
                 o = self.layers[j]
                 if o.get("weights_of") is not None:
                     raise ConfigError(f"{where}.weights_of={j}: that layer owns no tensors itself")
-                if (o["type"], o["mixer"], o.get("mlp")) != (L["type"], m, f):
-                    raise ConfigError(f"{where}: an entry with weights_of must equal layer {j}'s type, mixer and mlp")
+                if o["type"] != L["type"]:
+                    raise ConfigError(f"{where}: an entry with weights_of must have layer {j}'s type")
 
     # the names the engine asks every configuration for
     @property

@@ -41,7 +41,8 @@ def _mixer(L: dict, p: str, d: int, eps: float) -> PartSpec:
             position = PartSpec("none", "", {})
         mask = m.get("mask")
         return PartSpec("attention", f"{p}.mix", {
-            "d_model": d, "num_heads": m["heads"], "num_kv_heads": m["kv_heads"], "head_dim": m["dim"], "v_head_dim": m["vdim"],
+            "d_model": d, "num_heads": m["heads"], "num_kv_heads": m.get("kv_heads", m["heads"]), "head_dim": m["dim"],
+            "v_head_dim": m.get("vdim", m["dim"]),
             "position": position, "window": None if mask is None else mask["size"], "scale": m["scale"],
             "softcap": m.get("softcap"), "conv_taps": m.get("conv"), "gated": True, "qkv_bias": True,
             "names": {"q": "q", "k": "k", "v": "v", "o": "o", "g": "g"}, "weight_suffix": "", "bias_suffix": ".b",
