@@ -167,6 +167,10 @@ skinny_gemm_kernel(const SkinnyParams p) {
             if (EPI == 0) {
                 const float b = p.bias ? __bfloat162float(p.bias[row]) : 0.f;
                 reinterpret_cast<__nv_bfloat16*>(p.out)[(long long)m * p.ldo + row] = __float2bfloat16_rn(v[s] + b);
+            } else if (EPI == 4) {                                   // the square of relu, for feed-forwards of two matrices
+                const float b = p.bias ? __bfloat162float(p.bias[row]) : 0.f;
+                const float a = fmaxf(v[s] + b, 0.f);
+                reinterpret_cast<__nv_bfloat16*>(p.out)[(long long)m * p.ldo + row] = __float2bfloat16_rn(a * a);
             } else if (EPI == 1) {
                 reinterpret_cast<float*>(p.out)[((long long)split * p.M + m) * p.ldo + row] = v[s];
             } else {
@@ -208,7 +212,7 @@ int dispatch(const SkinnyParams& p, int splits, int unroll, cudaStream_t s) {
 
 extern "C" int ttie_skinny_max_rows() { return 64; }
 
-// epilogue: 0 bfloat16 out, 1 float32 partial sums [splits][M][N], 2 SwiGLU (w holds gate rows then up
+// epilogue: 0 bfloat16 out (4: the same after relu(.)^2), 1 float32 partial sums [splits][M][N], 2 SwiGLU (w holds gate rows then up
 // rows, N = F), 3 float32 out.  kslice: K range per CTA, a multiple of 128; splits = ceil(K / kslice),
 // which must be 1 unless epilogue is 1.
 extern "C" int ttie_skinny_gemm_tuned(const void* x, long long ldx, const void* w, long long ldw, const void* bias, void* out,
@@ -252,6 +256,7 @@ extern "C" int ttie_skinny_gemm_tuned(const void* x, long long ldx, const void* 
         case 1: return dispatch<1>(p, splits, unroll, s);
         case 2: return dispatch<2>(p, splits, unroll, s);
         case 3: return dispatch<3>(p, splits, unroll, s);
+        case 4: return dispatch<4>(p, splits, unroll, s);
     }
     TTIE_FAIL("skinny_gemm: unknown epilogue %d", epilogue);
 }

@@ -1080,7 +1080,16 @@ class CudaOps:
         return out
 
     def linear_act(self, x, w, act):
-        """act(x @ w.T) -> [M, N] in the compute dtype."""
+        """act(x @ w.T) -> [M, N] in the compute dtype.  Where the weight-streaming product takes the step (few rows,
+        bfloat16) the activation is its epilogue; else the product is followed by the activation kernel, in place."""
+        if act == "relu2" and self._skinny_ok(x, w):
+            M, K = x.shape
+            N = w.shape[0]
+            out = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+            self._check(self.lib.ttie_skinny_gemm(_ptr(x), x.stride(0), _ptr(w), w.stride(0), None, _ptr(out), N, M, N, K,
+                                                  math.ceil(K / 128) * 128, 4, 0, self._stream(x)), "skinny_gemm_relu2")
+            self.launches += 1
+            return out
         return self.activation(self.linear(x, w, None), act, inplace=True)
 
     # ---- gated linear units and routed experts
