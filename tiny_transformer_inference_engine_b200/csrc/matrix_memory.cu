@@ -30,11 +30,6 @@ namespace {
 
 __device__ __forceinline__ int slot_row_(int slot, int num_rows) { return slot < 0 ? num_rows - 1 : slot; }
 
-__device__ __forceinline__ float slice_sum(float v, int slices) {
-    for (int o = 1; o < slices; o <<= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-    return v;
-}
-
 template <typename T>
 __global__ void token_shift_mix_kernel(const T* __restrict__ x, long long ld, int T_, int d, int M, const float* __restrict__ mu,
                                        const float* __restrict__ prev, int prev_rows, const int* __restrict__ token_seq,
@@ -197,7 +192,6 @@ template <int SL> __device__ __forceinline__ float slices_sum(float v) {
     return v;
 }
 
-constexpr int MAXV = 16;            // staged tokens at most; also the most values of v (or gate weights) a thread carries ahead
 
 template <typename T, int KPT, int SL>
 __global__ void __launch_bounds__(128) wkv_scan_kernel(const WkvArgs a) {
@@ -256,10 +250,11 @@ __global__ void __launch_bounds__(128) wkv_scan_kernel(const WkvArgs a) {
         stage_rows<float>(w_s + buf * TB * a.Dpad, a.Dpad, wp + (size_t)c0 * HD, HD, nb, a.D, a.vec);
         cp_async_commit();
     };
-    float vreg[MAXV];                                                // this thread's share of the next run's v
+    constexpr int NV = TB >= SL ? TB / SL : 1;                       // a run's TB x cols values of v over the CTA's cols x SL threads
+    float vreg[NV];                                                  // this thread's share of the next run's v
     auto fetch_v = [&](int c0, int nb) {
 #pragma unroll
-        for (int i = 0; i < MAXV; ++i) {
+        for (int i = 0; i < NV; ++i) {
             const int e = i * blockDim.x + threadIdx.x;
             if (e < nb * cols) {
                 const int tt = e / cols, c = blockIdx.x * cols + (e - tt * cols);
@@ -274,7 +269,7 @@ __global__ void __launch_bounds__(128) wkv_scan_kernel(const WkvArgs a) {
         const bool more = c0 + TB < n;
         if (more) stage(buf ^ 1, c0 + TB, min(TB, n - c0 - TB));
 #pragma unroll
-        for (int i = 0; i < MAXV; ++i) {
+        for (int i = 0; i < NV; ++i) {
             const int e = i * blockDim.x + threadIdx.x;
             if (e < nb * cols) v_s[e] = vreg[i];
         }
@@ -449,10 +444,11 @@ __global__ void __launch_bounds__(128) mlstm_scan_kernel(const MlstmArgs a) {
         stage_rows<T>(k_s + buf * TB * a.Dpad, a.Dpad, kp + (size_t)c0 * a.ld, a.ld, nb, a.D, a.vec);
         cp_async_commit();
     };
-    float vreg[MAXV], greg[2] = {0.f, 0.f};                          // this thread's share of the next run's v and gate weights
+    constexpr int NV = TB >= SL ? TB / SL : 1;
+    float vreg[NV], greg[2] = {0.f, 0.f};                            // this thread's share of the next run's v and gate weights
     auto fetch_v = [&](int c0, int nb) {
 #pragma unroll
-        for (int i = 0; i < MAXV; ++i) {
+        for (int i = 0; i < NV; ++i) {
             const int e = i * blockDim.x + threadIdx.x;
             if (e < nb * cols) {
                 const int tt = e / cols, c = blockIdx.x * cols + (e - tt * cols);
@@ -472,7 +468,7 @@ __global__ void __launch_bounds__(128) mlstm_scan_kernel(const MlstmArgs a) {
         const bool more = c0 + TB < n;
         if (more) stage(buf ^ 1, c0 + TB, min(TB, n - c0 - TB));
 #pragma unroll
-        for (int i = 0; i < MAXV; ++i) {
+        for (int i = 0; i < NV; ++i) {
             const int e = i * blockDim.x + threadIdx.x;
             if (e < nb * cols) v_s[e] = vreg[i];
         }
@@ -650,7 +646,6 @@ extern "C" int ttie_wkv_scan(const void* r, const void* k, const void* v, long l
     const int cols = threads / a.slices;
     const int es = dtype == kF32 ? 4 : 2, ce = 16 / es;                // bytes per value of r and k; values per 16-byte copy
     a.tb = 64 / kpt;
-    if (threads * MAXV < a.tb * cols) TTIE_FAIL("wkv_scan: internal: %d threads cannot carry %d x %d values", threads, a.tb, cols);
     const size_t smem = (size_t)2 * a.tb * a.Dpad * (4 + 2 * es) + (size_t)a.tb * cols * 4;
     a.vec = D % ce == 0 && D % 4 == 0 && ld % ce == 0 && !(((uintptr_t)r | (uintptr_t)k | (uintptr_t)decay) & 15);
     dim3 grid(ceil_div(D, cols), H, num_seqs);
@@ -673,7 +668,7 @@ extern "C" int ttie_mlstm_scan(const void* q, const void* k, const void* v, long
     const int cols = threads / a.slices;
     const int es = dtype == kF32 ? 4 : 2, ce = 16 / es;
     a.tb = 64 / kpt;
-    if (threads * MAXV < a.tb * cols || 2 * threads < a.tb * 3) TTIE_FAIL("mlstm_scan: internal: %d threads cannot carry %d x %d values", threads, a.tb, cols);
+    if (2 * threads < a.tb * 3) TTIE_FAIL("mlstm_scan: internal: %d threads cannot carry the gate weights of %d tokens", threads, a.tb);
     const size_t smem = (size_t)2 * a.tb * a.Dpad * 2 * es + (size_t)a.tb * (cols + 3) * 4;
     a.vec = D % ce == 0 && ld % ce == 0 && !(((uintptr_t)q | (uintptr_t)k) & 15);
     dim3 grid(ceil_div(Dv, cols), H, num_seqs);
