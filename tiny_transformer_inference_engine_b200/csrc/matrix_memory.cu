@@ -192,10 +192,11 @@ template <int SL> __device__ __forceinline__ float slices_sum(float v) {
     return v;
 }
 
+constexpr int MAXV = 16;            // staged tokens at most; also the most values of v (or gate weights) a thread carries ahead
 
 template <typename T, int KPT, int SL>
 __global__ void __launch_bounds__(128) wkv_scan_kernel(const WkvArgs a) {
-    TTIE_PDL_ENTRY();
+    pdl_wait();                                                      // (the successor is let in at the end: its waiting CTAs would sit on the SMs of a long, latency-bound walk)
     extern __shared__ __align__(16) unsigned char smem_raw[];
     constexpr int TB = 64 / KPT;                                     // tokens per stage: 16, 8 or 4
     const int cols = blockDim.x / SL;
@@ -250,11 +251,10 @@ __global__ void __launch_bounds__(128) wkv_scan_kernel(const WkvArgs a) {
         stage_rows<float>(w_s + buf * TB * a.Dpad, a.Dpad, wp + (size_t)c0 * HD, HD, nb, a.D, a.vec);
         cp_async_commit();
     };
-    constexpr int NV = TB >= SL ? TB / SL : 1;                       // a run's TB x cols values of v over the CTA's cols x SL threads
-    float vreg[NV];                                                  // this thread's share of the next run's v
+    float vreg[MAXV];                                                // this thread's share of the next run's v
     auto fetch_v = [&](int c0, int nb) {
 #pragma unroll
-        for (int i = 0; i < NV; ++i) {
+        for (int i = 0; i < MAXV; ++i) {
             const int e = i * blockDim.x + threadIdx.x;
             if (e < nb * cols) {
                 const int tt = e / cols, c = blockIdx.x * cols + (e - tt * cols);
@@ -269,7 +269,7 @@ __global__ void __launch_bounds__(128) wkv_scan_kernel(const WkvArgs a) {
         const bool more = c0 + TB < n;
         if (more) stage(buf ^ 1, c0 + TB, min(TB, n - c0 - TB));
 #pragma unroll
-        for (int i = 0; i < NV; ++i) {
+        for (int i = 0; i < MAXV; ++i) {
             const int e = i * blockDim.x + threadIdx.x;
             if (e < nb * cols) v_s[e] = vreg[i];
         }
@@ -308,6 +308,7 @@ __global__ void __launch_bounds__(128) wkv_scan_kernel(const WkvArgs a) {
         __syncthreads();
     }
     }
+    pdl_launch_dependents();
     if (colv) {
 #pragma unroll
         for (int i = 0; i < KPT; i += 4) *reinterpret_cast<float4*>(sp + i) = make_float4(S[i], S[i + 1], S[i + 2], S[i + 3]);
@@ -387,7 +388,7 @@ struct MlstmArgs {
 
 template <typename T, int KPT, int SL>
 __global__ void __launch_bounds__(128) mlstm_scan_kernel(const MlstmArgs a) {
-    TTIE_PDL_ENTRY();
+    pdl_wait();                                                      // (the successor is let in at the end: its waiting CTAs would sit on the SMs of a long, latency-bound walk)
     extern __shared__ __align__(16) unsigned char smem_raw[];
     constexpr int TB = 64 / KPT;
     const int cols = blockDim.x / SL;
@@ -444,11 +445,10 @@ __global__ void __launch_bounds__(128) mlstm_scan_kernel(const MlstmArgs a) {
         stage_rows<T>(k_s + buf * TB * a.Dpad, a.Dpad, kp + (size_t)c0 * a.ld, a.ld, nb, a.D, a.vec);
         cp_async_commit();
     };
-    constexpr int NV = TB >= SL ? TB / SL : 1;
-    float vreg[NV], greg[2] = {0.f, 0.f};                            // this thread's share of the next run's v and gate weights
+    float vreg[MAXV], greg[2] = {0.f, 0.f};                          // this thread's share of the next run's v and gate weights
     auto fetch_v = [&](int c0, int nb) {
 #pragma unroll
-        for (int i = 0; i < NV; ++i) {
+        for (int i = 0; i < MAXV; ++i) {
             const int e = i * blockDim.x + threadIdx.x;
             if (e < nb * cols) {
                 const int tt = e / cols, c = blockIdx.x * cols + (e - tt * cols);
@@ -468,7 +468,7 @@ __global__ void __launch_bounds__(128) mlstm_scan_kernel(const MlstmArgs a) {
         const bool more = c0 + TB < n;
         if (more) stage(buf ^ 1, c0 + TB, min(TB, n - c0 - TB));
 #pragma unroll
-        for (int i = 0; i < NV; ++i) {
+        for (int i = 0; i < MAXV; ++i) {
             const int e = i * blockDim.x + threadIdx.x;
             if (e < nb * cols) v_s[e] = vreg[i];
         }
@@ -517,6 +517,7 @@ __global__ void __launch_bounds__(128) mlstm_scan_kernel(const MlstmArgs a) {
         __syncthreads();
     }
     }
+    pdl_launch_dependents();
     if (colv) {
 #pragma unroll
         for (int i = 0; i < KPT; i += 4) *reinterpret_cast<float4*>(sp + i) = make_float4(S[i], S[i + 1], S[i + 2], S[i + 3]);
@@ -646,6 +647,7 @@ extern "C" int ttie_wkv_scan(const void* r, const void* k, const void* v, long l
     const int cols = threads / a.slices;
     const int es = dtype == kF32 ? 4 : 2, ce = 16 / es;                // bytes per value of r and k; values per 16-byte copy
     a.tb = 64 / kpt;
+    if (threads * MAXV < a.tb * cols) TTIE_FAIL("wkv_scan: internal: %d threads cannot carry %d x %d values", threads, a.tb, cols);
     const size_t smem = (size_t)2 * a.tb * a.Dpad * (4 + 2 * es) + (size_t)a.tb * cols * 4;
     a.vec = D % ce == 0 && D % 4 == 0 && ld % ce == 0 && !(((uintptr_t)r | (uintptr_t)k | (uintptr_t)decay) & 15);
     dim3 grid(ceil_div(D, cols), H, num_seqs);
@@ -668,7 +670,7 @@ extern "C" int ttie_mlstm_scan(const void* q, const void* k, const void* v, long
     const int cols = threads / a.slices;
     const int es = dtype == kF32 ? 4 : 2, ce = 16 / es;
     a.tb = 64 / kpt;
-    if (2 * threads < a.tb * 3) TTIE_FAIL("mlstm_scan: internal: %d threads cannot carry the gate weights of %d tokens", threads, a.tb);
+    if (threads * MAXV < a.tb * cols || 2 * threads < a.tb * 3) TTIE_FAIL("mlstm_scan: internal: %d threads cannot carry %d x %d values", threads, a.tb, cols);
     const size_t smem = (size_t)2 * a.tb * a.Dpad * 2 * es + (size_t)a.tb * (cols + 3) * 4;
     a.vec = D % ce == 0 && ld % ce == 0 && !(((uintptr_t)q | (uintptr_t)k) & 15);
     dim3 grid(ceil_div(Dv, cols), H, num_seqs);
